@@ -10,7 +10,7 @@ Here one object serves a batch:
   and values in pages of 64 tokens taken from the group's pool as the sequence grows (K page
   ``[kv_head][token][key width]``, V page ``[kv_head][value width][token]``, in the group's own
   storage type when its mixer asks for one); a group with a window gives pages
-  back once every token in them is older than the window.  A "state" group holds a fixed-size
+  back once every token in them is older than the window (pages that hold a sequence's kept first tokens stay).  A "state" group holds a fixed-size
   tensor per slot, zeroed when a sequence opens;
 * an execution that reads another execution's cache gets a view of that storage and never writes;
 * one slot and one page per group beyond those the pools hand out (``idle_slot``, ``idle_page``): a
@@ -65,6 +65,7 @@ class CacheGroup:
         n = len(self.entries)
         if self.kind == "kv":
             self.window = need.window
+            self.keep_first = int(need.keep_first or 0) if need.window else 0
             self.pages = IdPool(n_pages, "page")
             dtype = need.dtype or runtime.dtype
             # one page more than the pool hands out: the cache's idle page
@@ -73,6 +74,7 @@ class CacheGroup:
             self.state = None
         elif self.kind == "state":
             self.window = None
+            self.keep_first = 0
             self.pages = None
             self.k = self.v = None
             self.state = torch.zeros((n, n_slots + 1, *need.state_shape), dtype=need.state_dtype,
@@ -187,7 +189,8 @@ class ModelCache:
             if g.window:
                 oldest_needed = new_length - g.window + 1       # first key the next query may see
                 pages = seq.pages[g.index]
-                for p in range(len(pages)):
+                kept_pages = (g.keep_first + PAGE - 1) // PAGE  # pages that hold the sequence's kept first tokens stay
+                for p in range(kept_pages, len(pages)):
                     if pages[p] >= 0 and PAGE * p + PAGE - 1 < oldest_needed:
                         g.pages.free(pages[p])
                         pages[p] = -1

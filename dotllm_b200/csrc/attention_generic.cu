@@ -34,7 +34,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
                          const int32_t* __restrict__ block_table, int bt_stride, int nh, int nkv, int hd, int vd,
                          float scale, int window, float softcap, const float* __restrict__ slopes,
-                         const T* __restrict__ gate, int gate_stride) {
+                         const T* __restrict__ gate, int gate_stride, int keep_first, const float* __restrict__ sinks) {
     extern __shared__ float q_smem[];                 // [AG_WARPS][hd]
     const int lane = threadIdx.x;
     const int t = blockIdx.x;
@@ -49,6 +49,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int seq = token_seq[t];
     const int kvh = h / (nh / nkv);
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int kept = min(keep_first, first);          // keys before the window that stay visible: the sequence's first tokens
+    const int window_tile = (first / 32) * 32;
     const float slope = slopes != nullptr ? slopes[h] : 0.f;
     const int32_t* pages = block_table + (size_t)seq * bt_stride;
 
@@ -57,12 +59,13 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.f;
 
-    for (int j0 = (first / 32) * 32; j0 <= pos; j0 += 32) {
+    for (int j0 = kept > 0 ? 0 : window_tile; j0 <= pos; j0 += 32) {
+        if (j0 >= kept && j0 < window_tile) { j0 = window_tile - 32; continue; }      // between the kept tokens and the window: nothing is seen
         const int page = pages[j0 / DL_PAGE];
         if (page < 0 || page >= n_pages) continue;    // host-validated; never read outside the pool
         const int in_page0 = j0 % DL_PAGE;
         const int j = j0 + lane;
-        const bool valid = (j >= first) && (j <= pos);
+        const bool valid = (j >= first || j < kept) && (j <= pos);
         float s = -INFINITY;
         if (valid) {
             const T* kr = k_pool + dl_k_offset(page, nkv, kvh, in_page0 + lane, hd);
@@ -87,13 +90,14 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 for (int kk = 0; kk < 32; ++kk) {
                     const float pk = __shfl_sync(0xffffffffu, p, kk);
                     // masked keys are never read: a reused page may hold anything there
-                    if (j0 + kk >= first && j0 + kk <= pos && d < vd) a += pk * dl_to_f32<T>(vrow[kk]);
+                    if ((j0 + kk >= first || j0 + kk < kept) && j0 + kk <= pos && d < vd) a += pk * dl_to_f32<T>(vrow[kk]);
                 }
                 acc[i] = a;
             }
         }
     }
-    float inv = 1.0f / l;
+    // a sink: one more term exp(sink_h) in the denominator, with no key and no value
+    float inv = 1.0f / (sinks != nullptr ? l + expf(sinks[h] - m) : l);
     if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-dl_to_f32<T>(gate[(size_t)t * gate_stride + h])));
     T* orow = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
@@ -123,7 +127,7 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
                                 const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
                                 const int32_t* __restrict__ block_table, int bt_stride, int nh, int nkv, int hd, int vd,
                                 float scale, int window, float softcap, const float* __restrict__ slopes,
-                                const T* __restrict__ gate, int gate_stride) {
+                                const T* __restrict__ gate, int gate_stride, int keep_first, const float* __restrict__ sinks) {
     extern __shared__ float ag_smem[];                // [AG_WARPS][hd] queries, [32][hd + 1] keys, [vd][33] values
     const int lane = threadIdx.x, tid = threadIdx.y * 32 + threadIdx.x;
     const int t = blockIdx.x;
@@ -138,6 +142,8 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
     const int seq = token_seq[t];
     const int kvh = (blockIdx.y * AG_WARPS) / (nh / nkv);      // the same for the block's four heads
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int kept = min(keep_first, first);          // keys before the window that stay visible: the sequence's first tokens
+    const int window_tile = (first / 32) * 32;
     const float slope = slopes != nullptr ? slopes[h] : 0.f;
     const int32_t* pages = block_table + (size_t)seq * bt_stride;
 
@@ -146,7 +152,8 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.f;
 
-    for (int j0 = (first / 32) * 32; j0 <= pos; j0 += 32) {
+    for (int j0 = kept > 0 ? 0 : window_tile; j0 <= pos; j0 += 32) {
+        if (j0 >= kept && j0 < window_tile) { j0 = window_tile - 32; continue; }      // between the kept tokens and the window: nothing is seen
         const int page = pages[j0 / DL_PAGE];
         if (page < 0 || page >= n_pages) continue;    // host-validated; the same for every thread of the block
         const int in_page0 = j0 % DL_PAGE;
@@ -164,11 +171,11 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
                 kx[b] = vx[b] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (idx < n_kvec) {
                     const int key = idx / hd4, c = idx - key * hd4;
-                    if (j0 + key >= first && j0 + key <= pos) kx[b] = ag_load4<T>(kbase + (size_t)key * hd + 4 * c);   // masked keys are never read
+                    if ((j0 + key >= first || j0 + key < kept) && j0 + key <= pos) kx[b] = ag_load4<T>(kbase + (size_t)key * hd + 4 * c);   // masked keys are never read
                 }
                 if (idx < n_vvec) {
                     const int d = idx >> 3, kq = idx & 7;
-                    if (j0 + 4 * kq + 3 >= first && j0 + 4 * kq <= pos) vx[b] = ag_load4<T>(vbase + (size_t)d * DL_PAGE + 4 * kq);
+                    if ((j0 + 4 * kq + 3 >= first || j0 + 4 * kq < kept) && j0 + 4 * kq <= pos) vx[b] = ag_load4<T>(vbase + (size_t)d * DL_PAGE + 4 * kq);
                 }
             }
 #pragma unroll
@@ -188,7 +195,7 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
         }
         __syncthreads();
         const int j = j0 + lane;
-        const bool valid = (j >= first) && (j <= pos);
+        const bool valid = (j >= first || j < kept) && (j <= pos);
         float s = -INFINITY;
         if (valid) {
             const float* kr = kt + lane * (hd + 1);
@@ -211,13 +218,14 @@ attention_generic_shared_kernel(const T* __restrict__ q, int q_stride, T* __rest
                 const float* vrow = vt + (size_t)(d < vd ? d : 0) * 33;
                 for (int kk = 0; kk < 32; ++kk) {
                     const float pk = __shfl_sync(0xffffffffu, p, kk);
-                    if (j0 + kk >= first && j0 + kk <= pos && d < vd) a += pk * vrow[kk];
+                    if ((j0 + kk >= first || j0 + kk < kept) && j0 + kk <= pos && d < vd) a += pk * vrow[kk];
                 }
                 acc[i] = a;
             }
         }
     }
-    float inv = 1.0f / l;
+    // a sink: one more term exp(sink_h) in the denominator, with no key and no value
+    float inv = 1.0f / (sinks != nullptr ? l + expf(sinks[h] - m) : l);
     if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-dl_to_f32<T>(gate[(size_t)t * gate_stride + h])));
     T* orow = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
@@ -232,7 +240,7 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
                                     const int32_t* token_seq, const int32_t* token_pos,
                                     const int32_t* block_table, int bt_stride, int n_tokens, int nh, int nkv,
                                     int hd, int vd, float scale, int window, float softcap, const float* slopes,
-                                    const void* gate, int gate_stride, void* stream) {
+                                    const void* gate, int gate_stride, int keep_first, const float* sinks, void* stream) {
     DL_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0 && vd > 0 && n_pages > 0, "attention: bad sizes");
     DL_REQUIRE(vd <= AG_MAX_HD, "attention: value width %d exceeds the supported maximum %d", vd, AG_MAX_HD);
     DL_REQUIRE(gate == nullptr || gate_stride >= nh, "attention: a row of gate logits holds one per query head");
@@ -240,6 +248,7 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
     DL_REQUIRE(hd <= AG_MAX_HD, "attention: head_dim %d exceeds the supported maximum %d", hd, AG_MAX_HD);
     DL_REQUIRE(q_stride >= nh * hd && out_stride >= nh * vd, "attention: row strides shorter than the rows");
     DL_REQUIRE(window >= 0, "attention: window must be 0 (none) or positive");
+    DL_REQUIRE(keep_first >= 0, "attention: the number of kept first tokens cannot be negative");
     DL_REQUIRE(softcap >= 0.f, "attention: softcap must be 0 (none) or positive");
     if (n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
@@ -252,12 +261,12 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
             attention_generic_shared_kernel<float><<<grid, block, shared_smem, s>>>(
                 (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
                 n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd, scale, window, softcap, slopes,
-                (const float*)gate, gate_stride);
+                (const float*)gate, gate_stride, keep_first, sinks);
         else
             attention_generic_shared_kernel<__nv_bfloat16><<<grid, block, shared_smem, s>>>(
                 (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
                 (const __nv_bfloat16*)v_pool, n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd,
-                scale, window, softcap, slopes, (const __nv_bfloat16*)gate, gate_stride);
+                scale, window, softcap, slopes, (const __nv_bfloat16*)gate, gate_stride, keep_first, sinks);
         DL_CHECK_LAUNCH("attention_generic");
         return DL_OK;
     }
@@ -266,12 +275,12 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
         attention_generic_kernel<float><<<grid, block, smem, s>>>(
             (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
             n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd, scale, window, softcap, slopes,
-                (const float*)gate, gate_stride);
+                (const float*)gate, gate_stride, keep_first, sinks);
     else if (dtype == DL_BF16)
         attention_generic_kernel<__nv_bfloat16><<<grid, block, smem, s>>>(
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, vd,
-            scale, window, softcap, slopes, (const __nv_bfloat16*)gate, gate_stride);
+            scale, window, softcap, slopes, (const __nv_bfloat16*)gate, gate_stride, keep_first, sinks);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "attention: dtype %d", dtype);
     DL_CHECK_LAUNCH("attention_generic");

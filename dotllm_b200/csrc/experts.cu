@@ -21,19 +21,60 @@
 #define EX_OUT_PER_BLOCK 64
 
 // logits float32 [rows, E] (the router's product), bias float32 [E] or NULL.  A warp per row.
+// scoring 2: the weights are the chosen experts' shares of the softmax over ALL experts, not renormalised.  With
+// `groups` > 0 the experts lie in that many equal runs of neighbours; a run's score is its largest logit, and only the
+// experts of the `keep_groups` best runs (ties to the lower index) can be chosen.
 __global__ void __launch_bounds__(32 * EX_WARPS)
 route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ bias, int32_t* __restrict__ ids,
-                  float* __restrict__ weights, int rows, int E, int top, int scoring) {
-    extern __shared__ float route_smem[];            // per warp: E logits, then `top` chosen values
+                  float* __restrict__ weights, int rows, int E, int top, int scoring, int groups, int keep_groups) {
+    extern __shared__ float route_smem[];            // per warp: E logits, then `top` chosen values, then `groups` run scores
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * EX_WARPS + warp;
     if (row >= rows) return;                          // warps are independent below
-    float* logits = route_smem + (size_t)warp * (E + top);
+    float* logits = route_smem + (size_t)warp * (E + top + groups);
     float* chosen = logits + E;
-    for (int e = lane; e < E; e += 32) logits[e] = z[(size_t)row * z_stride + e] + (bias != nullptr ? bias[e] : 0.f);
+    float* run_best = chosen + top;
+    float all_max = -INFINITY, all_sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        logits[e] = z[(size_t)row * z_stride + e] + (bias != nullptr ? bias[e] : 0.f);
+        all_max = fmaxf(all_max, logits[e]);
+    }
     __syncwarp();
+    if (scoring == 2) {                               // the softmax's denominator over every expert, before any is ruled out
+        all_max = dl_warp_max(all_max);
+        for (int e = lane; e < E; e += 32) all_sum += expf(logits[e] - all_max);
+        all_sum = dl_warp_sum(all_sum);
+    }
+    if (groups > 0 && keep_groups < groups) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float best = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, logits[e]);
+            run_best[g] = best;
+        }
+        __syncwarp();
+        for (int j = 0; j < keep_groups; ++j) {       // mark the best runs by +inf in their score's place
+            float best = -INFINITY;
+            int at = groups;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = run_best[g];
+                if (v != INFINITY && (at == groups || v > best)) { best = v; at = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (oa < groups && (at == groups || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+            }
+            if (lane == 0 && at < groups) run_best[at] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (run_best[e / per] != INFINITY) logits[e] = -INFINITY;
+        __syncwarp();
+    }
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
         int at = E;
@@ -59,6 +100,10 @@ route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __rest
             for (int j = 0; j < top; ++j) weights[(size_t)row * top + j] = 1.0f / (1.0f + expf(-chosen[j]));
             return;
         }
+        if (scoring == 2) {
+            for (int j = 0; j < top; ++j) weights[(size_t)row * top + j] = expf(chosen[j] - all_max) / all_sum;
+            return;
+        }
         const float m = chosen[0];
         float sum = 0.f;
         for (int j = 0; j < top; ++j) sum += expf(chosen[j] - m);
@@ -68,15 +113,18 @@ route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __rest
 
 // z float32 [rows, E], rows z_stride apart; bias float32 [E] or NULL; ids int32 [rows, top]; weights float32 [rows, top].
 extern "C" int dl_route_topk(const float* z, int z_stride, const float* bias, int32_t* ids, float* weights, int rows, int E,
-                             int top, int scoring, void* stream) {
+                             int top, int scoring, int groups, int keep_groups, void* stream) {
     DL_REQUIRE(rows >= 0 && E > 0 && top > 0 && top <= E && z_stride >= E, "route_topk: bad sizes E=%d top=%d", E, top);
-    DL_REQUIRE(scoring == 0 || scoring == 1, "route_topk: scoring %d (0: softmax over the chosen, 1: sigmoid)", scoring);
-    const size_t smem = (size_t)EX_WARPS * (E + top) * sizeof(float);
+    DL_REQUIRE(scoring >= 0 && scoring <= 2, "route_topk: scoring %d (0: softmax over the chosen, 1: sigmoid, 2: softmax over all)", scoring);
+    DL_REQUIRE(groups >= 0 && (groups == 0 || (E % groups == 0 && keep_groups > 0 && keep_groups <= groups &&
+                                               top <= keep_groups * (E / groups))),
+               "route_topk: %d experts in %d runs of which %d stay cannot give %d choices", E, groups, keep_groups, top);
+    const size_t smem = (size_t)EX_WARPS * (E + top + groups) * sizeof(float);
     DL_REQUIRE(smem <= 48 * 1024, "route_topk: %d experts are more than the kernel's shared memory takes", E);
     if (rows == 0) return DL_OK;
     const dim3 grid((rows + EX_WARPS - 1) / EX_WARPS), block(32 * EX_WARPS);
     cudaError_t e = dl_launch_dependent(route_topk_kernel, grid, block, smem, (cudaStream_t)stream, z, z_stride, bias, ids, weights,
-                                        rows, E, top, scoring);
+                                        rows, E, top, scoring, groups, keep_groups);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "route_topk: %s", cudaGetErrorString(e));
     return DL_OK;
 }

@@ -200,12 +200,13 @@ extern "C" int dl_gla_scan(const void* q, const void* k, const void* v, int ld, 
     return dl_fail(DL_ERR_UNSUPPORTED, "gla_scan: dtype %d", dtype);
 }
 
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * gain[:] * silu(g[t, h, :]): one warp per (token, head).
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * gain[:] * gate(g[t, h, :]): one warp per (token, head).
+// gate_kind 0: silu(g); 1: sigmoid(g).
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, int o_stride, const T* __restrict__ g, int g_stride,
                       const float* __restrict__ gain, T* __restrict__ out, int out_stride, int rows, int H, int vdim,
-                      float eps) {
+                      float eps, int gate_kind) {
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int lane = threadIdx.x & 31;
@@ -221,13 +222,15 @@ head_norm_gate_kernel(const float* __restrict__ o, int o_stride, const T* __rest
     T* dst = out + (size_t)t * out_stride + (size_t)h * vdim;
     for (int j = lane; j < vdim; j += 32) {
         const float gate = dl_to_f32<T>(grow[j]);
-        dst[j] = dl_from_f32<T>(orow[j] * scale * gain[j] * (gate * (1.0f / (1.0f + expf(-gate)))));
+        const float sig = 1.0f / (1.0f + expf(-gate));
+        dst[j] = dl_from_f32<T>(orow[j] * scale * gain[j] * (gate_kind == 1 ? sig : gate * sig));
     }
 }
 
 extern "C" int dl_head_norm_gate(const float* o, int o_stride, const void* g, int g_stride, const float* gain, void* out,
-                                 int out_stride, int dtype, int rows, int H, int vdim, float eps, void* stream) {
+                                 int out_stride, int dtype, int rows, int H, int vdim, float eps, int gate_kind, void* stream) {
     DL_REQUIRE(rows >= 0 && H > 0 && vdim > 0 && eps > 0.f, "head_norm_gate: bad arguments");
+    DL_REQUIRE(gate_kind == 0 || gate_kind == 1, "head_norm_gate: gate kind %d (0: silu, 1: sigmoid)", gate_kind);
     if (rows == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const long warps = (long)rows * H;
@@ -235,10 +238,10 @@ extern "C" int dl_head_norm_gate(const float* o, int o_stride, const void* g, in
     cudaError_t e;
     if (dtype == DL_F32)
         e = dl_launch_dependent(head_norm_gate_kernel<float>, grid, block, 0, s, o, o_stride, (const float*)g, g_stride, gain,
-                                (float*)out, out_stride, rows, H, vdim, eps);
+                                (float*)out, out_stride, rows, H, vdim, eps, gate_kind);
     else if (dtype == DL_BF16)
         e = dl_launch_dependent(head_norm_gate_kernel<__nv_bfloat16>, grid, block, 0, s, o, o_stride, (const __nv_bfloat16*)g,
-                                g_stride, gain, (__nv_bfloat16*)out, out_stride, rows, H, vdim, eps);
+                                g_stride, gain, (__nv_bfloat16*)out, out_stride, rows, H, vdim, eps, gate_kind);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "head_norm_gate: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "head_norm_gate: %s", cudaGetErrorString(e));

@@ -264,3 +264,51 @@ extern "C" int dl_add_rows(float* a, const float* b, int rows, int width, void* 
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "add_rows: %s", cudaGetErrorString(e));
     return DL_OK;
 }
+
+// RMS norm of every head of a row on its own, with a gain shared by the heads: queries and keys before they meet.
+//   y[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * gain[:]
+// The row holds heads_a heads under gain_a and, behind them, heads_b heads under gain_b (a stacked projection's
+// queries and keys), each `dim` wide.  One warp per (row, head); statistics and the product in float32.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_rmsnorm_kernel(const T* __restrict__ x, int x_stride, T* __restrict__ y, int y_stride, const float* __restrict__ gain_a,
+                    const float* __restrict__ gain_b, int rows, int heads_a, int heads_b, int dim, float eps) {
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int lane = threadIdx.x & 31, heads = heads_a + heads_b;
+    const long idx = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (idx >= (long)rows * heads) return;
+    const int t = (int)(idx / heads), h = (int)(idx % heads);
+    const T* src = x + (size_t)t * x_stride + (size_t)h * dim;
+    T* dst = y + (size_t)t * y_stride + (size_t)h * dim;
+    const float* gain = h < heads_a ? gain_a : gain_b;
+    float ss = 0.f;
+    for (int j = lane; j < dim; j += 32) { const float v = dl_to_f32<T>(src[j]); ss += v * v; }
+    ss = dl_warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int j = lane; j < dim; j += 32) dst[j] = dl_from_f32<T>(dl_to_f32<T>(src[j]) * scale * gain[j]);
+}
+
+// x, y [rows, (heads_a + heads_b) * dim] of `dtype`, rows x_stride / y_stride apart; gain_a, gain_b float32 [dim]
+// (gain_b may be NULL when heads_b is 0).
+extern "C" int dl_head_rmsnorm(const void* x, int x_stride, void* y, int y_stride, int dtype, const float* gain_a,
+                               const float* gain_b, int rows, int heads_a, int heads_b, int dim, float eps, void* stream) {
+    DL_REQUIRE(rows >= 0 && heads_a >= 0 && heads_b >= 0 && heads_a + heads_b > 0 && dim > 0 && eps > 0.f, "head_rmsnorm: bad sizes");
+    DL_REQUIRE(gain_a != nullptr && (heads_b == 0 || gain_b != nullptr), "head_rmsnorm: a gain is missing");
+    const int width = (heads_a + heads_b) * dim;
+    DL_REQUIRE(x_stride >= width && y_stride >= width, "head_rmsnorm: rows overlap");
+    if (rows == 0) return DL_OK;
+    const long warps = (long)rows * (heads_a + heads_b);
+    const dim3 grid((unsigned)((warps + 3) / 4)), block(128);
+    cudaError_t e;
+    if (dtype == DL_F32)
+        e = dl_launch_dependent(head_rmsnorm_kernel<float>, grid, block, 0, (cudaStream_t)stream, (const float*)x, x_stride,
+                                (float*)y, y_stride, gain_a, gain_b, rows, heads_a, heads_b, dim, eps);
+    else if (dtype == DL_BF16)
+        e = dl_launch_dependent(head_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, (cudaStream_t)stream, (const __nv_bfloat16*)x,
+                                x_stride, (__nv_bfloat16*)y, y_stride, gain_a, gain_b, rows, heads_a, heads_b, dim, eps);
+    else
+        return dl_fail(DL_ERR_UNSUPPORTED, "head_rmsnorm: dtype %d", dtype);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "head_rmsnorm: %s", cudaGetErrorString(e));
+    return DL_OK;
+}

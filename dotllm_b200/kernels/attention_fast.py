@@ -166,9 +166,11 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
 
 
 def run(q, q_stride, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
-        n_heads, n_kv_heads, head_dim, scale, window, plan):
+        n_heads, n_kv_heads, head_dim, scale, window, plan, keep_first=0, sinks=None):
     """Run a tensor-core kernel into ``out`` and return True, or return False to let the
-    generic kernel take the call."""
+    generic kernel take the call (kept first tokens and sinks are the generic kernel's)."""
+    if keep_first or sinks is not None:
+        return False
     if q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16 or head_dim not in DECODE_HEAD_DIMS:
         return False
     if plan.all_single and q.shape[0] == plan.n_seqs:

@@ -22,8 +22,11 @@ _library.register_signatures({
     "dl_add_rows": [_P, _P, _I, _I, _P],
     "dl_gated_activation": [_P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P],
     "dl_gla_scan": [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
-    "dl_head_norm_gate": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
-    "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "dl_head_norm_gate": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "dl_head_rmsnorm": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
+    "dl_delta_rule": [_P, _I, _P, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, ctypes.c_long, _I,
+                      _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
     "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P],
     "dl_expert_sort": [_P, _I, _I, _P, _P, _I, _P],
@@ -371,7 +374,7 @@ class ScoreHook:
 
 
 def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
-              head_dim, scale, window=0, plan=None, score_hook=None, value_dim=None, gate=None):
+              head_dim, scale, window=0, plan=None, score_hook=None, value_dim=None, gate=None, keep_first=0, sinks=None):
     """Causal attention of the step's tokens over their sequences' cached keys and values.
 
     q [T, nh*hd] (row-contiguous view); returns [T, nh*vd] of q's dtype (vd = ``value_dim``, default hd).
@@ -379,9 +382,15 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
     (sequence lengths, chunking) that the tensor-core kernels need; without one, for sizes
     they do not take (values of another width than the keys among them), or with a ``score_hook``, the generic
     kernel runs.  ``gate`` [T, nh] of q's dtype (a column view is fine): head h's output is multiplied by
-    sigmoid(gate[t, h]) - in the generic kernel's last step, or by ``head_gate`` behind a tensor-core kernel."""
+    sigmoid(gate[t, h]) - in the generic kernel's last step, or by ``head_gate`` behind a tensor-core kernel.
+    ``keep_first`` n > 0 (with a window): a sequence's first n keys stay visible when the window has passed them.
+    ``sinks`` float32 [nh]: head h's softmax has one more term exp(sinks[h]) in its denominator, with no key and no value."""
     vd = int(value_dim or head_dim)
-    _need_cuda(q, k_pool, v_pool, token_seq, token_pos, block_table, gate)
+    _need_cuda(q, k_pool, v_pool, token_seq, token_pos, block_table, gate, sinks)
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (n_heads,) or not sinks.is_contiguous()):
+        raise KernelError(f"attention: the sinks must be contiguous float32 [{n_heads}]")
+    if keep_first < 0 or (keep_first and not window):
+        raise KernelError("attention: kept first tokens need a window (and cannot be negative)")
     T = q.shape[0]
     gs = 0
     if gate is not None:
@@ -406,24 +415,25 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
             raise KernelError(f"attention: a score hook's slopes must be contiguous float32 [{n_heads}] on the device")
     if plan is not None and q.dtype == torch.bfloat16 and not score_hook and vd == head_dim:
         if attention_fast.run(q, qs, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
-                              n_heads, n_kv_heads, head_dim, float(scale), int(window), plan):
+                              n_heads, n_kv_heads, head_dim, float(scale), int(window), plan,
+                              keep_first=int(keep_first), sinks=sinks):
             return out if gate is None else head_gate(out, gate, n_heads, vd)
     _library.call("dl_attention_generic", _ptr(q), qs, _ptr(out), out.stride(0), _code(q.dtype),
                   _ptr(k_pool), _ptr(v_pool), n_pages, _ptr(token_seq), _ptr(token_pos),
                   _ptr(block_table), block_table.shape[1], T, n_heads, n_kv_heads, head_dim, vd,
-                  float(scale), int(window), float(softcap), _ptr(slopes), _ptr(gate), gs, _stream())
+                  float(scale), int(window), float(softcap), _ptr(slopes), _ptr(gate), gs, int(keep_first), _ptr(sinks), _stream())
     return out
 
 
 def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
                          n_heads, n_kv_heads, head_dim, scale, window=0, plan=None, score_hook=None,
-                         value_dim=None, biases=None, gate=None):
+                         value_dim=None, biases=None, gate=None, keep_first=0, sinks=None):
     """``rope_cache_write`` followed by ``attention`` (same arguments, same result).  A bfloat16
     decode step (one new token per sequence) with a full-width rotation of head size 64 or 128, or
     with no rotation, runs as one kernel that adds the biases, rotates q, puts the new keys and values into the
     cache, attends and gates the heads; everything else runs the kernels one after the other."""
     if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and not score_hook and (value_dim or head_dim) == head_dim \
-            and (k is not None or biases is not None or gate is not None):
+            and (k is not None or biases is not None or gate is not None) and not keep_first and sinks is None:
         out = attention_fast.decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads,
                                           n_kv_heads, head_dim, float(scale), int(window), plan, biases=biases, gate=gate)
         if out is not None:
@@ -431,7 +441,8 @@ def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, bl
     rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
                      n_heads, n_kv_heads, head_dim, write_cache=k is not None, value_dim=value_dim, biases=biases)
     return attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
-                     scale, window, plan=plan, score_hook=score_hook, value_dim=value_dim, gate=gate)
+                     scale, window, plan=plan, score_hook=score_hook, value_dim=value_dim, gate=gate,
+                     keep_first=keep_first, sinks=sinks)
 
 
 def qkv_rope_cache(x, w_qkv, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
@@ -520,9 +531,15 @@ def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_sca
     return out
 
 
-def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype):
+HEAD_GATES = {"silu": 0, "sigmoid": 1}
+
+
+def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype, gate="silu"):
     """Each head's rows of o (float32 [T, H*vdim]) divided by their root mean square, times ``gain``
-    (float32 [vdim], shared by the heads), times silu(g) (g [T, H*vdim] of ``out_dtype``, a column view is fine)."""
+    (float32 [vdim], shared by the heads), times silu(g) or (``gate`` "sigmoid") sigmoid(g) (g [T, H*vdim] of
+    ``out_dtype``, a column view is fine)."""
+    if gate not in HEAD_GATES:
+        raise KernelError(f"head_norm_gate: unknown gate {gate!r}; known: {sorted(HEAD_GATES)}")
     _need_cuda(o, g, gain)
     T = o.shape[0]
     gs = _rows_view(g, "head_norm_gate g")
@@ -531,18 +548,79 @@ def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype):
         raise KernelError("head_norm_gate: o float32 [T, H*vdim], g of the output's dtype and shape, gain float32 [vdim]")
     out = torch.empty((T, n_heads * vdim), dtype=out_dtype, device=o.device)
     _library.call("dl_head_norm_gate", _ptr(o), o.stride(0), _ptr(g), gs, _ptr(gain), _ptr(out), out.stride(0),
-                  _code(out_dtype), T, n_heads, vdim, float(eps), _stream())
+                  _code(out_dtype), T, n_heads, vdim, float(eps), HEAD_GATES[gate], _stream())
+    return out
+
+
+def head_rmsnorm(x, gain_a, heads_a, dim, eps, gain_b=None, heads_b=0):
+    """Every head of a row normalised on its own: y[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * gain[:].  The
+    row holds ``heads_a`` heads under ``gain_a`` and behind them ``heads_b`` heads under ``gain_b`` (queries and keys of
+    one stacked projection), each ``dim`` wide; x may be a column view.  Returns a new tensor of x's dtype."""
+    _need_cuda(x, gain_a, gain_b)
+    T, width = x.shape[0], (heads_a + heads_b) * dim
+    if x.dim() != 2 or x.shape[1] != width:
+        raise KernelError(f"head_rmsnorm: x must be [T, {width}]")
+    for g, n in ((gain_a, heads_a), (gain_b, heads_b)):
+        if n and (g is None or g.dtype != torch.float32 or g.shape != (dim,) or not g.is_contiguous()):
+            raise KernelError(f"head_rmsnorm: a gain must be contiguous float32 [{dim}]")
+    out = torch.empty((T, width), dtype=x.dtype, device=x.device)
+    _library.call("dl_head_rmsnorm", _ptr(x), _rows_view(x, "head_rmsnorm x"), _ptr(out), out.stride(0), _code(x.dtype),
+                  _ptr(gain_a), _ptr(gain_b), T, int(heads_a), int(heads_b), int(dim), float(eps), _stream())
+    return out
+
+
+# ------------------------------------------------------------------ delta rule
+def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, memory, n_heads, n_kv_heads, dim, vdim,
+               q_scale, unit_eps):
+    """The gated delta rule with a decay per key channel over each sequence's new rows in order.
+
+    x [T, >= C]: the stacked projection, its first C = 2*G*dim + H*vdim columns the channels of q, k (G = ``n_kv_heads``
+    heads of ``dim``) and v (H = ``n_heads`` heads of ``vdim``); ``taps`` [C, K] of x's dtype: a causal convolution over
+    time per channel, then silu; q and k unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times ``q_scale``;
+    beta = sigmoid(b_logit) [T, H]; g = exp(-exp(a_log[h]) softplus(z + dt_bias)) with z float32 [T, H*dim].  Per head
+    (query/key head h // (H/G)): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+    ``memory`` float32 [slots, H*dim*vdim + (K-1)*C]: per slot the states and behind them the convolution's last K - 1
+    inputs; read and updated.  Returns o float32 [T, H*vdim]."""
+    _need_cuda(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, memory)
+    T = x.shape[0]
+    H, G = int(n_heads), int(n_kv_heads)
+    C, K = 2 * G * dim + H * vdim, taps.shape[1]
+    ld = _rows_view(x, "delta_rule x")
+    if x.shape[1] < C or taps.shape != (C, K) or taps.dtype != x.dtype or not taps.is_contiguous():
+        raise KernelError(f"delta_rule: x must hold {C} channels and the taps be [{C}, K] of its dtype")
+    if b_logit.shape != (T, H) or b_logit.dtype != x.dtype or z.shape != (T, H * dim) or z.dtype != torch.float32:
+        raise KernelError("delta_rule: b_logit [T, H] of x's dtype, z float32 [T, H*dim]")
+    for t, n, what in ((dt_bias, H * dim, "dt_bias"), (a_log, H, "a_log")):
+        if t.dtype != torch.float32 or t.shape != (n,) or not t.is_contiguous():
+            raise KernelError(f"delta_rule: {what} must be contiguous float32 [{n}]")
+    n_state = H * dim * vdim
+    if memory.dtype != torch.float32 or memory.dim() != 2 or memory.shape[1] != n_state + (K - 1) * C or memory.stride(1) != 1:
+        raise KernelError(f"delta_rule: a slot's memory must be float32 [{n_state + (K - 1) * C}]")
+    _int32(token_seq, "delta_rule token_seq")
+    _int32(cu_new, "delta_rule cu_new")
+    _int32(slots, "delta_rule slots")
+    f32 = dict(dtype=torch.float32, device=x.device)
+    qo, ko = torch.empty((T, G * dim), **f32), torch.empty((T, G * dim), **f32)
+    vo, go = torch.empty((T, H * vdim), **f32), torch.empty((T, H * dim), **f32)
+    bo, out = torch.empty((T, H), **f32), torch.empty((T, H * vdim), **f32)
+    _library.call("dl_delta_rule", _ptr(x), ld, _ptr(taps), K, _code(x.dtype), _ptr(b_logit), _rows_view(b_logit, "delta_rule b"),
+                  _ptr(z), _rows_view(z, "delta_rule z"), _ptr(dt_bias), _ptr(a_log), _ptr(token_seq), _ptr(cu_new), _ptr(slots),
+                  memory.data_ptr(), memory.data_ptr() + 4 * n_state, memory.stride(0), memory.shape[0],
+                  _ptr(qo), _ptr(ko), _ptr(vo), _ptr(go), _ptr(bo), _ptr(out), slots.numel(), T, H, G, int(dim), int(vdim),
+                  float(q_scale), float(unit_eps), _stream())
     return out
 
 
 # ---------------------------------------------------------------------- experts
-ROUTER_SCORINGS = {"softmax_chosen": 0, "sigmoid": 1}
+ROUTER_SCORINGS = {"softmax_chosen": 0, "sigmoid": 1, "softmax_all": 2}
 
 
-def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False):
+def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False, groups=None):
     """The ``top`` experts with the largest float32 logits x R^T + bias per row (ties: the lower index) and their
     weights: the softmax over the chosen logits alone (``scoring`` "softmax_chosen"), or each chosen expert's own
-    sigmoid(logit), not renormalised ("sigmoid").  ``experts``: the first that many rows of ``w_router`` are the
+    sigmoid(logit), not renormalised ("sigmoid"), or its share of the softmax over all experts, not renormalised
+    ("softmax_all").  ``groups`` (count, keep): the experts lie in ``count`` equal runs of neighbours, a run scores its
+    largest logit, and only the experts of the ``keep`` best runs can be chosen.  ``experts``: the first that many rows of ``w_router`` are the
     experts' (default all); rows behind them ride the same product (a per-token gate, say) and only show in the logits.
     Returns (ids int32 [T, top], weights float32 [T, top]), and the float32 logits [T, rows of w_router] behind them
     ``with_logits``."""
@@ -559,12 +637,15 @@ def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, w
         raise KernelError(f"route_topk: the bias must be float32 [{E}]")
     if not 0 < top <= E:
         raise KernelError(f"route_topk: cannot choose {top} of {E} experts")
+    n_groups, keep_groups = (int(groups[0]), int(groups[1])) if groups else (0, 0)
+    if groups and (n_groups <= 0 or E % n_groups or not 0 < keep_groups <= n_groups or top > keep_groups * (E // n_groups)):
+        raise KernelError(f"route_topk: {E} experts in {n_groups} runs of which {keep_groups} stay cannot give {top} choices")
     T = x.shape[0]
     z = linear(x, w_router, out_dtype=torch.float32, resident=True)         # float32 accumulation, float32 logits
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
     _library.call("dl_route_topk", _ptr(z), z.stride(0) if T > 1 else rows_w, _ptr(bias), _ptr(ids), _ptr(weights), T, E, top,
-                  ROUTER_SCORINGS[scoring], _stream())
+                  ROUTER_SCORINGS[scoring], n_groups, keep_groups, _stream())
     return (ids, weights, z) if with_logits else (ids, weights)
 
 

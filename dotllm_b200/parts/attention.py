@@ -12,7 +12,10 @@ biases on the three projections (added in float32 by the kernel that rotates and
 (token, query head) from a projection of the mixer's input (``gate`` "head_sigmoid": the head's output times
 sigmoid of its logit, before the output projection; the gate's rows ride the stacked product), and an execution
 that reads another execution's keys and values (the schedule's ``cache_of``: such a layer has no key and value
-projections, ``own_kv`` False).
+projections, ``own_kv`` False); values that are the keys as projected, before any norm or rotation (``values`` "keys": no
+value projection); an RMS norm of every query and key head before the rotation, with one gain for the queries and one for
+the keys (``qk_norm``); a window that keeps a sequence's first tokens visible (``keep_first``); and a learned number per
+head in the softmax's denominator, a sink without key or value (``sink``).
 
 Keys and values of different widths on the tensor cores.  The tensor-core attention kernels take one width for keys
 and values (32, 64, 96 or 128).  In a bfloat16 run a mixer with these options whose widths differ, or are equal and none of
@@ -54,10 +57,14 @@ class AttentionMixer(Mixer):
     softmax, which sends the mixer to the generic attention kernel); optional ``value_dim`` (per head, default
     ``head_dim``), ``bias`` (True: q, k and v have biases), ``gate`` (None or "head_sigmoid"), ``own_kv`` (False: no key
     and value projections, the layer reads another's cache) and ``tensors``: the local names of ``q``, ``k``, ``v``,
-    ``o``, ``gate`` and the bias suffix ``bias`` (appended to a projection's name)."""
+    ``o``, ``gate`` and the bias suffix ``bias`` (appended to a projection's name); optional ``values`` ("own", or "keys":
+    v is k as projected, there is no value projection and ``value_dim`` is ``head_dim``), ``qk_norm`` ({"eps"}: tensors
+    ``q_norm``, ``k_norm`` [head_dim]), ``keep_first`` (with a window: that many first tokens of a sequence stay visible) and
+    ``sink`` (True: tensor ``sink`` [n_heads], exp(sink_h) joins head h's softmax denominator)."""
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-             "gate": "g_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias"}
+             "gate": "g_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks"}
     GATES = (None, "head_sigmoid")
     ROW_STEP = 16                # the stacked matrix's rows are a multiple of this: its product's rows stay 16-byte aligned
 
@@ -87,19 +94,34 @@ class AttentionMixer(Mixer):
         if self.gate not in self.GATES:
             raise ConfigError(f"attention: unknown gate {self.gate!r}; known: {list(self.GATES)}")
         self.own_kv = bool(params.get("own_kv", True))
+        self.values = params.get("values", "own")
+        if self.values not in ("own", "keys"):
+            raise ConfigError(f"attention: values are 'own' or 'keys', not {self.values!r}")
+        if self.values == "keys" and (self.value_dim != self.head_dim or self.bias):
+            raise ConfigError("attention: values that are the keys have the keys' width and no biases")
+        qk_norm = params.get("qk_norm")
+        self.qk_norm_eps = float(qk_norm["eps"]) if qk_norm else None
+        self.sink = bool(params.get("sink", False))
+        self.keep_first = int(params.get("keep_first") or 0)
+        if self.keep_first < 0 or (self.keep_first and not self.window):
+            raise ConfigError("attention: kept first tokens need a window (and cannot be negative)")
+        self.q_gain = self.k_gain = self.sinks = None
         self.names = dict(self.NAMES, **(params.get("tensors") or {}))
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv_heads * self.head_dim
         self.v_width = self.n_kv_heads * self.value_dim
         self.o_dim = self.n_heads * self.value_dim
         # the reference's block as it is (one matrix of q, k and v rows, nothing added): its fused paths apply
-        self.plain = not self.bias and self.gate is None and self.value_dim == self.head_dim and self.own_kv
+        self.plain = not self.bias and self.gate is None and self.value_dim == self.head_dim and self.own_kv \
+            and self.values == "own" and self.qk_norm_eps is None and not self.sink and not self.keep_first
+        # heads keep their own width and channel order where a norm runs over them or the keys double as values
+        as_stored = self.values == "keys" or self.qk_norm_eps is not None
         self.w_qkv = None
         self.w_o = None
         self.biases = None
         # the width every head is laid out at (see the module's text); head_dim / value_dim stay the stored widths
         self.lay_k, self.lay_v = self.head_dim, self.value_dim
-        if runtime.dtype == torch.bfloat16 and not self.plain and \
+        if runtime.dtype == torch.bfloat16 and not self.plain and not as_stored and \
                 (self.value_dim != self.head_dim or self.head_dim not in self.TENSOR_CORE_WIDTHS):
             fits = [w for w in self.TENSOR_CORE_WIDTHS if w >= max(self.head_dim, self.value_dim)]
             if fits and self.n_heads // self.n_kv_heads <= 16:
@@ -107,7 +129,7 @@ class AttentionMixer(Mixer):
         # a partial rotation spread over the whole head (see the module's text): fused_rotary() gives (cos, sin, r)
         fused = self.position.fused_rotary()
         rd = int(fused[2]) if fused is not None else 0
-        self.spread = bool(runtime.dtype == torch.bfloat16 and not self.plain and self.lay_k == self.lay_v
+        self.spread = bool(runtime.dtype == torch.bfloat16 and not self.plain and not as_stored and self.lay_k == self.lay_v
                            and self.lay_k in self.TENSOR_CORE_WIDTHS and 0 < rd < self.lay_k)
         self.rotation = None if fused is None else (self._wide_tables(fused[0], fused[1], rd, self.lay_k) + (self.lay_k,)
                                                     if self.spread else fused)
@@ -161,7 +183,8 @@ class AttentionMixer(Mixer):
         specs = {n["q"]: WeightSpec((self.q_dim, h))}
         if self.own_kv:
             specs[n["k"]] = WeightSpec((self.kv_dim, h))
-            specs[n["v"]] = WeightSpec((self.v_width, h))
+            if self.values == "own":
+                specs[n["v"]] = WeightSpec((self.v_width, h))
         if self.bias:
             specs[n["q_bias"]] = WeightSpec((self.q_dim,), "precise", ("normal", 0.1))
             if self.own_kv:
@@ -169,6 +192,12 @@ class AttentionMixer(Mixer):
                 specs[n["v_bias"]] = WeightSpec((self.v_width,), "precise", ("normal", 0.1))
         if self.gate:
             specs[n["gate"]] = WeightSpec((self.n_heads, h), init=("normal", 0.1))
+        if self.qk_norm_eps is not None:
+            specs[n["q_norm"]] = WeightSpec((self.head_dim,), "precise", ("one_plus_uniform", 0.1))
+            if self.own_kv:
+                specs[n["k_norm"]] = WeightSpec((self.head_dim,), "precise", ("one_plus_uniform", 0.1))
+        if self.sink:
+            specs[n["sink"]] = WeightSpec((self.n_heads,), "precise", ("normal", 1.0))
         specs[n["o"]] = WeightSpec((h, self.o_dim))
         return specs
 
@@ -177,7 +206,9 @@ class AttentionMixer(Mixer):
         H, G, hd, vd, lk, lv = self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim, self.lay_k, self.lay_v
         rows = [self._reorder(self._widen(tensors[n["q"]], H, hd, lk), H)]
         if self.own_kv:
-            rows += [self._reorder(self._widen(tensors[n["k"]], G, hd, lk), G), self._widen(tensors[n["v"]], G, vd, lv)]
+            rows.append(self._reorder(self._widen(tensors[n["k"]], G, hd, lk), G))
+            if self.values == "own":
+                rows.append(self._widen(tensors[n["v"]], G, vd, lv))
         if self.gate:
             rows.append(tensors[n["gate"]])
         if not self.plain:
@@ -187,6 +218,11 @@ class AttentionMixer(Mixer):
                 rows.append(torch.zeros((pad, self.hidden_size), dtype=rows[0].dtype, device=rows[0].device))
         self.w_qkv = torch.cat(rows, dim=0).contiguous()
         self.w_o = self._widen(tensors[n["o"]], H, vd, lv, dim=1).contiguous()
+        if self.qk_norm_eps is not None:
+            self.q_gain = tensors[n["q_norm"]].contiguous()
+            self.k_gain = tensors[n["k_norm"]].contiguous() if self.own_kv else None
+        if self.sink:
+            self.sinks = tensors[n["sink"]].contiguous()
         if self.bias:
             self.biases = (self._reorder(self._widen(tensors[n["q_bias"]], H, hd, lk), H).contiguous(),
                            self._reorder(self._widen(tensors[n["k_bias"]], G, hd, lk), G).contiguous() if self.own_kv else None,
@@ -197,7 +233,7 @@ class AttentionMixer(Mixer):
 
     def cache_need(self):
         return CacheNeed("kv", n_kv_heads=self.n_kv_heads, head_dim=self.lay_k, window=self.window,
-                         v_dim=self.lay_v if self.lay_v != self.lay_k else None)
+                         v_dim=self.lay_v if self.lay_v != self.lay_k else None, keep_first=self.keep_first)
 
     takes_scaled_rows = True                    # x goes straight into the Q/K/V product
 
@@ -213,9 +249,18 @@ class AttentionMixer(Mixer):
         y = ops.linear(x, self.w_qkv, resident=True)
         q, at = y[:, :qd], qd
         k = v = None
-        if self.own_kv:
+        if self.own_kv and self.values == "keys":
+            k, at = y[:, at:at + kvd], at + kvd
+            v = k                                   # as projected: the norm below writes its result elsewhere
+        elif self.own_kv:
             k, v, at = y[:, at:at + kvd], y[:, at + kvd:at + kvd + vw], at + kvd + vw
         g = y[:, at:at + self.n_heads] if self.gate else None
+        if self.qk_norm_eps is not None:
+            if self.own_kv:
+                normed = ops.head_rmsnorm(y[:, :qd + kvd], self.q_gain, self.n_heads, lk, self.qk_norm_eps, self.k_gain, self.n_kv_heads)
+                q, k = normed[:, :qd], normed[:, qd:]
+            else:
+                q = ops.head_rmsnorm(q, self.q_gain, self.n_heads, lk, self.qk_norm_eps)
         fused = self.rotation
         if fused is None:
             if self.biases is not None:
@@ -230,7 +275,7 @@ class AttentionMixer(Mixer):
                                      self.n_heads, self.n_kv_heads, lk, self.scale,
                                      int(self.window or 0), plan=step.attention_plan,
                                      score_hook=self.score_hook if self.score_hook else None,
-                                     value_dim=lv, biases=self.biases, gate=g)
+                                     value_dim=lv, biases=self.biases, gate=g, keep_first=self.keep_first, sinks=self.sinks)
         return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
 
     def forward(self, x, step, cache_view):

@@ -56,7 +56,7 @@ class CacheNeed:
     """What one execution of a mixer keeps per sequence.
 
     kind "kv": keys and values per token, ``n_kv_heads`` x ``head_dim`` each; ``window`` None
-    keeps every token, an integer keeps the last ``window``.  ``k_dim`` / ``v_dim`` give keys and
+    keeps every token, an integer keeps the last ``window`` and, with ``keep_first`` n, the sequence's first n.  ``k_dim`` / ``v_dim`` give keys and
     values widths of their own (a compressed or latent cache) and ``dtype`` a storage type of its own
     (default: the run's); the built-in attention kernels take equal widths in the run's type, a mixer
     with other needs reads and writes its pages itself.
@@ -72,6 +72,7 @@ class CacheNeed:
     k_dim: Optional[int] = None
     v_dim: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    keep_first: int = 0
 
     def key_width(self):
         return self.k_dim or self.head_dim
@@ -81,7 +82,8 @@ class CacheNeed:
 
     def group_key(self, run_dtype):
         if self.kind == "kv":
-            return ("kv", self.n_kv_heads, self.key_width(), self.value_width(), self.window, self.dtype or run_dtype)
+            return ("kv", self.n_kv_heads, self.key_width(), self.value_width(), self.window, self.dtype or run_dtype,
+                    self.keep_first if self.window else 0)
         return ("state", tuple(self.state_shape), self.state_dtype)
 
 
@@ -264,7 +266,7 @@ def registered(family):
 
 def _ensure_builtin():
     from . import (norms, rotary, attention, feed_forward, blocks, embedding, linear_attention,  # noqa: F401
-                   latent_attention, experts)
+                   latent_attention, experts, delta_rule)
 
 
 def make_part(family, spec, hidden_size, runtime):

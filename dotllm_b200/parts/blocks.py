@@ -52,5 +52,29 @@ class SandwichNormBlock(Arrangement):
         return residual, self.feed_forward_post_norm.branch(self.feed_forward.forward(n))
 
 
+class ParallelBlock(Arrangement):
+    """One norm, two sublayers that both read its output, one addition: h = norm(x); x += mixer(h) + ff(h).  The
+    feed-forward may be absent.  The mixer's output joins the stream at once (its last product adds itself where it
+    can); the feed-forward's is handed on as the pending branch, so the stream gets x + mixer + ff in float32."""
+    needs = ("norm", "mixer")
+    narrows = True
+
+    def forward(self, residual, pending, step, cache_view, keep_rows=None):
+        from ..kernels import ops
+        n = ops.resolve(normalised_for(None, self.norm, residual, pending))     # a plain tensor: two parts read it
+        a = self.mixer.forward(n, step, cache_view)         # every token: the cache needs all keys, values and states
+        if keep_rows is not None:
+            residual = ops.gather_rows(residual, keep_rows)
+            a = ops.narrow_rows(a, keep_rows)
+            if "feed_forward" in self.parts:
+                n = ops.gather_rows(n, keep_rows, out_dtype=n.dtype)
+        if "feed_forward" not in self.parts:
+            return residual, a
+        if not (isinstance(a, ops.PendingProduct) and a.add_into(residual)):
+            ops.add_rows(residual, ops.resolve(a).to(residual.dtype))
+        return residual, self.feed_forward.forward(n)
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("parallel", ParallelBlock)
 register_arrangement("sandwich_norm", SandwichNormBlock)

@@ -26,8 +26,10 @@ class RoutedExperts(FeedForward):
     """params: ``n_experts``, ``top``, ``intermediate_size`` (of one expert), ``activation`` (one of
     ``ops.GATINGS``) with ``limit`` and ``alpha``; ``router_bias`` (default True); ``shared``: None or
     {"intermediate_size", "limit", "gate"} (same activation and alpha; ``gate`` True: the shared expert's output is
-    multiplied by sigmoid of a per-token logit, tensor ``shared_gate`` [1, H]); ``scoring`` ("softmax_chosen" or
-    "sigmoid") and ``weight_on`` ("output" or "input"); optional ``tensors``: local name patterns ``expert`` (with
+    multiplied by sigmoid of a per-token logit, tensor ``shared_gate`` [1, H]); ``scoring`` ("softmax_chosen",
+    "sigmoid", or "softmax_all": a chosen expert's share of the softmax over all experts, not renormalised),
+    ``groups`` (None or (count, keep): the experts lie in ``count`` equal runs of neighbours, a run scores its best expert,
+    and only the experts of the ``keep`` best runs can be chosen) and ``weight_on`` ("output" or "input"); optional ``tensors``: local name patterns ``expert`` (with
     {e} and {m} for the expert's index and gate / up / down), ``router``, ``router_bias``, ``shared`` (with {m}),
     ``shared_gate``."""
 
@@ -52,6 +54,12 @@ class RoutedExperts(FeedForward):
         self.scoring = params.get("scoring", "softmax_chosen")
         if self.scoring not in ops.ROUTER_SCORINGS:
             raise ConfigError(f"routed experts: unknown scoring {self.scoring!r}; known: {sorted(ops.ROUTER_SCORINGS)}")
+        groups = params.get("groups")
+        self.groups = (int(groups[0]), int(groups[1])) if groups else None
+        if self.groups and (self.groups[0] <= 0 or self.n_experts % self.groups[0] or not 0 < self.groups[1] <= self.groups[0]
+                            or self.top > self.groups[1] * (self.n_experts // self.groups[0])):
+            raise ConfigError(f"routed experts: {self.n_experts} experts in {self.groups[0]} groups of which {self.groups[1]} "
+                              f"stay cannot give {self.top} choices")
         self.weight_on = params.get("weight_on", "output")
         if self.weight_on not in ("output", "input"):
             raise ConfigError(f"routed experts: weight_on is 'output' or 'input', not {self.weight_on!r}")
@@ -119,7 +127,7 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x):
         ids, weights, z = ops.route_topk(x, self.w_router, self.b_router, self.top, scoring=self.scoring,
-                                         experts=self.n_experts, with_logits=True)
+                                         experts=self.n_experts, with_logits=True, groups=self.groups)
         shared = shared_gate = None
         if self.shared_ff:
             if self.gated:

@@ -82,11 +82,54 @@ def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_sca
     return out
 
 
-def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype):
+def head_norm_gate(o, g, gain, n_heads, vdim, eps, out_dtype, gate="silu"):
     T = o.shape[0]
     y = _rms(o.view(T, n_heads, vdim), eps) * gain
     gf = g.to(torch.float32).reshape(T, n_heads, vdim)
-    return (y * gf * torch.sigmoid(gf)).reshape(T, n_heads * vdim).to(out_dtype)
+    act = torch.sigmoid(gf) if gate == "sigmoid" else gf * torch.sigmoid(gf)
+    return (y * act).reshape(T, n_heads * vdim).to(out_dtype)
+
+
+def head_rmsnorm(x, gain_a, heads_a, dim, eps, gain_b=None, heads_b=0):
+    T = x.shape[0]
+    xf = x.to(torch.float32).reshape(T, heads_a + heads_b, dim)
+    y = _rms(xf, eps)
+    y = torch.cat([y[:, :heads_a] * gain_a] + ([y[:, heads_a:] * gain_b] if heads_b else []), dim=1)
+    return y.reshape(T, -1).to(x.dtype)
+
+
+def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, memory, n_heads, n_kv_heads, dim, vdim,
+               q_scale, unit_eps):
+    """Sequence by sequence, token by token, from and into the slot's memory (states, then the convolution's history)."""
+    T, H, G = x.shape[0], n_heads, n_kv_heads
+    C, K = taps.shape
+    n_state = H * dim * vdim
+    out = torch.zeros((T, H * vdim), dtype=torch.float32, device=x.device)
+    tf = taps.to(torch.float32)
+    for b in range(slots.numel()):
+        mem = memory[int(slots[b])]
+        S = mem[:n_state].view(H, dim, vdim)
+        hist = mem[n_state:].view(K - 1, C)
+        for t in range(int(cu_new[b]), int(cu_new[b + 1])):
+            now = x[t, :C].to(torch.float32)
+            window = torch.cat([hist, now[None]], dim=0)                    # the K inputs the taps meet, oldest first
+            y = (window * tf.T).sum(dim=0)
+            y = y * torch.sigmoid(y)
+            if K > 1:
+                hist.copy_(window[1:].clone())
+            q = y[:G * dim].view(G, dim)
+            k = y[G * dim:2 * G * dim].view(G, dim)
+            v = y[2 * G * dim:].view(H, vdim)
+            q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * q_scale
+            k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+            q, k = q.repeat_interleave(H // G, dim=0), k.repeat_interleave(H // G, dim=0)
+            beta = torch.sigmoid(b_logit[t].to(torch.float32))
+            g = torch.exp(-torch.exp(a_log)[:, None] * torch.nn.functional.softplus((z[t] + dt_bias).view(H, dim)))
+            S.mul_(g[:, :, None])
+            u = beta[:, None] * (v - torch.einsum("hdv,hd->hv", S, k))
+            S.add_(k[:, :, None] * u[:, None, :])
+            out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+    return out
 
 
 def unary_activation(x, kind):
@@ -109,11 +152,23 @@ def head_gate(o, gate, n_heads, width):
     return o
 
 
-def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False):
+def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False, groups=None):
     logits = x.to(torch.float32) @ w_router.to(torch.float32).T
     z = logits[:, :experts] if experts is not None else logits
     if bias is not None:
         z = z + bias
+    share = torch.softmax(z, dim=-1)                        # over every expert, before any is ruled out
+    if groups:
+        count, keep = groups
+        left = z.reshape(z.shape[0], count, -1).max(dim=-1).values
+        kept = torch.zeros_like(left, dtype=torch.bool)
+        for _ in range(keep):                               # the best runs one by one, ties to the lower index
+            best = left.max(dim=-1).values
+            at = (left == best[:, None]).to(torch.int32).argmax(dim=-1)
+            kept = kept.scatter(1, at[:, None], True)
+            left = left.scatter(1, at[:, None], float("-inf"))
+        out_of_reach = (~kept).repeat_interleave(z.shape[1] // count, dim=1)
+        z = z.masked_fill(out_of_reach, float("-inf"))
     ids = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
     vals = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
     for j in range(top):                                   # ties go to the lower index
@@ -121,7 +176,10 @@ def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, w
         at = (z == best[:, None]).to(torch.int32).argmax(dim=-1)
         ids[:, j], vals[:, j] = at, best
         z = z.scatter(1, at[:, None], float("-inf"))
-    weights = torch.sigmoid(vals) if scoring == "sigmoid" else torch.softmax(vals, dim=-1)
+    if scoring == "softmax_all":
+        weights = torch.gather(share, 1, ids.long())
+    else:
+        weights = torch.sigmoid(vals) if scoring == "sigmoid" else torch.softmax(vals, dim=-1)
     return (ids, weights, logits) if with_logits else (ids, weights)
 
 
@@ -197,12 +255,19 @@ def gather_kv(k_pool, v_pool, pages, length):
     return torch.stack(ks).to(torch.float32), torch.stack(vs).to(torch.float32)
 
 
+def _gather_some(k_pool, v_pool, pages, positions):
+    """Keys and values of the listed positions only (a page that a window gave back is never touched)."""
+    ks = [k_pool[int(pages[j // PAGE]), :, j % PAGE, :] for j in positions]
+    vs = [v_pool[int(pages[j // PAGE]), :, :, j % PAGE] for j in positions]
+    return torch.stack(ks).to(torch.float32), torch.stack(vs).to(torch.float32)
+
+
 def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
-              head_dim, scale, window=0, plan=None, score_hook=None, value_dim=None, gate=None):
+              head_dim, scale, window=0, plan=None, score_hook=None, value_dim=None, gate=None, keep_first=0, sinks=None):
     vd = value_dim or head_dim
-    if score_hook or vd != head_dim or gate is not None:
+    if score_hook or vd != head_dim or gate is not None or keep_first or sinks is not None:
         return _attention_general(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
-                                  scale, window, score_hook, vd, gate)
+                                  scale, window, score_hook, vd, gate, keep_first, sinks)
     T = q.shape[0]
     out = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=q.device)
     for t in range(T):
@@ -223,25 +288,30 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
 
 
 def _attention_general(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim, scale,
-                       window, hook, vd, gate):
+                       window, hook, vd, gate, keep_first=0, sinks=None):
     """Scores capped (softcap * tanh(s / softcap)) and then biased by slope * (key - query position); values of
-    their own width; a head's output times sigmoid of its gate logit."""
+    their own width; a head's output times sigmoid of its gate logit; a sequence's first ``keep_first`` keys visible
+    beyond the window; a sink per head in the denominator."""
     T = q.shape[0]
     out = torch.empty((T, n_heads * vd), dtype=torch.float32, device=q.device)
     group = n_heads // n_kv_heads
     for t in range(T):
         pos = int(token_pos[t])
         first = max(0, pos - window + 1) if window else 0
-        k, v = gather_kv(k_pool, v_pool, block_table[int(token_seq[t])], pos + 1)
+        seen = list(range(min(keep_first, first))) + list(range(first, pos + 1))
+        k, v = _gather_some(k_pool, v_pool, block_table[int(token_seq[t])], seen)
         for h in range(n_heads):
             qh = q[t, h * head_dim:(h + 1) * head_dim].to(torch.float32)
-            s = (k[first:, h // group] @ qh) * scale
+            s = (k[:, h // group] @ qh) * scale
             if hook and hook.softcap > 0:
                 s = hook.softcap * torch.tanh(s / hook.softcap)
             if hook and hook.slopes is not None:
-                s = s + float(hook.slopes[h]) * (torch.arange(first, pos + 1, dtype=torch.float32) - pos)
-            w = torch.softmax(s, dim=0)
-            o = w @ v[first:, h // group]
+                s = s + float(hook.slopes[h]) * (torch.tensor(seen, dtype=torch.float32) - pos)
+            if sinks is None:
+                w = torch.softmax(s, dim=0)
+            else:                                           # one more term in the denominator, nothing in the numerator
+                w = torch.softmax(torch.cat([s, sinks[h:h + 1].to(torch.float32)]), dim=0)[:-1]
+            o = w @ v[:, h // group]
             out[t, h * vd:(h + 1) * vd] = o if gate is None else o * torch.sigmoid(gate[t, h].to(torch.float32))
     return out.to(q.dtype)
 
