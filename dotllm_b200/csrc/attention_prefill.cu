@@ -87,7 +87,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_row0,
                          const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_new,
                          const int32_t* __restrict__ cu_new, const int32_t* __restrict__ block_table,
-                         int bt_stride, int nh, int nkv, float scale, int window, int* __restrict__ status) {
+                         int bt_stride, int nh, int nkv, float scale, int window, int keep_first,
+                         const float* __restrict__ sinks, int* __restrict__ status) {
     constexpr int DC = HD / 32;
     constexpr int DT = HD / 8;
     constexpr int PAGE_ELEMS = DL_PAGE * HD;
@@ -111,7 +112,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int blk_pos_min = start + tile_row, blk_pos_max = start + tile_row + rows_here - 1;
     const int blk_first = (window > 0 && blk_pos_min - window + 1 > 0) ? blk_pos_min - window + 1 : 0;
     const int page_lo = blk_first / DL_PAGE, page_hi = blk_pos_max / DL_PAGE;
-    const int n_blk_pages = page_hi - page_lo + 1;
+    // with a window, a sequence's first keep_first keys stay visible: their pages, where the window has passed them, come
+    // first in the block's list of pages, then the window's; page n of the list is page page_of(n) of the sequence
+    const int kept_pages = (window > 0 && keep_first > 0) ? min((keep_first + DL_PAGE - 1) / DL_PAGE, page_lo) : 0;
+    const int n_blk_pages = kept_pages + page_hi - page_lo + 1;
+    auto page_of = [&](int n) { return n < kept_pages ? n : page_lo + (n - kept_pages); };
     const int32_t* pages = block_table + (size_t)b * bt_stride;
 
     if (threadIdx.x == 0) {
@@ -130,7 +135,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             int n = 0;
             for (; n < n_blk_pages; ++n) {
                 const int s = n % AP_STAGES;
-                const int page = pages[page_lo + n];
+                const int page = pages[page_of(n)];
                 if (page < 0 || page >= n_pages) { gave_up = 1; atomicExch(status, 2); break; }   // host-validated
                 if (n >= AP_STAGES && !ap_mbar_wait(&empty_bar[s], ((n / AP_STAGES) - 1) & 1, &gave_up)) {
                     if (!gave_up) atomicExch(status, 1);
@@ -185,9 +190,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                 gave_up = 1;
                 break;
             }
-            const int base = (page_lo + n) * DL_PAGE;        // first key of the page
+            const int base = page_of(n) * DL_PAGE;           // first key of the page
             // pages wholly outside what this warp's rows may see are only released
-            if (base <= warp_pos_max && base + DL_PAGE > warp_first) {
+            if (base <= warp_pos_max && (base + DL_PAGE > warp_first || base < keep_first)) {
                 __nv_bfloat16* kp = stage_mem + (size_t)s * 2 * PAGE_ELEMS;
                 const uint32_t k_addr = ap_smem(kp) + (uint32_t)((8 * (g >> 1) + (g & 1)) * HD + t * 8) * 2u;
                 const uint32_t v_addr = ap_smem(kp + PAGE_ELEMS) + (uint32_t)(g * DL_PAGE + t * 8) * 2u;
@@ -233,8 +238,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int key = base + 32 * hh + 8 * t + 2 * j + e;
-                                if (key > pos_lo || key < first_lo) sc[hh][j][e] = -INFINITY;
-                                if (key > pos_hi || key < first_hi) sc[hh][j][2 + e] = -INFINITY;
+                                if (key > pos_lo || (key < first_lo && key >= keep_first)) sc[hh][j][e] = -INFINITY;
+                                if (key > pos_hi || (key < first_hi && key >= keep_first)) sc[hh][j][2 + e] = -INFINITY;
                             }
                 }
                 float mx_lo = -INFINITY, mx_hi = -INFINITY;
@@ -320,6 +325,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
             l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
             l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+            // a sink: one more term exp(sink_h) in the denominator (maxima are in units of log2), with no key and no value
+            const float sink2 = sinks != nullptr ? sinks[h] * 1.4426950408889634f : 0.f;
+            if (sinks != nullptr) {
+                l_lo += ap_ex2(sink2 - m_lo);
+                l_hi += ap_ex2(sink2 - m_hi);
+            }
             const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
             __nv_bfloat16* o_lo = out + (size_t)(tok0 + g) * out_stride + (size_t)h * HD;
             __nv_bfloat16* o_hi = out + (size_t)(tok0 + g + 8) * out_stride + (size_t)h * HD;
@@ -338,7 +349,7 @@ static int ap_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, voi
                      const void* k_pool, const void* v_pool, int n_pages, const int32_t* tile_seq,
                      const int32_t* tile_row0, const int32_t* seq_start, const int32_t* seq_new,
                      const int32_t* cu_new, const int32_t* block_table, int bt_stride, int nh, int nkv, float scale,
-                     int window, int* status) {
+                     int window, int keep_first, const float* sinks, int* status) {
     const size_t smem = (size_t)AP_STAGES * 2 * DL_PAGE * HD * 2;
     static bool configured = false;
     if (!configured) {
@@ -349,7 +360,7 @@ static int ap_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, voi
     attention_prefill_kernel<HD><<<grid, AP_THREADS, smem, s>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
         (const __nv_bfloat16*)v_pool, n_pages, tile_seq, tile_row0, seq_start, seq_new, cu_new, block_table, bt_stride,
-        nh, nkv, scale, window, status);
+        nh, nkv, scale, window, keep_first, sinks, status);
     DL_CHECK_LAUNCH("attention_prefill");
     return DL_OK;
 }
@@ -357,15 +368,18 @@ static int ap_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, voi
 // q, out: bf16 [T, nh*hd] packed new tokens of all sequences.  tile_seq / tile_row0: for every
 // 128-row tile its sequence and its first row among that sequence's new tokens.  seq_start,
 // seq_new: cached length before the step and new tokens, per sequence; cu_new: packed offsets.
-// status: int32, set non-zero if a wait expired.
+// keep_first: with a window, that many first keys of a sequence stay visible.  sinks: float32 [nh] or NULL, exp(sinks[h])
+// joins head h's softmax denominator.  status: int32, set non-zero if a wait expired.
 extern "C" int dl_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
                                          const void* k_pool, const void* v_pool, int n_pages,
                                          const int32_t* tile_seq, const int32_t* tile_row0, int n_tiles,
                                          const int32_t* seq_start, const int32_t* seq_new, const int32_t* cu_new,
                                          const int32_t* block_table, int bt_stride, int nh, int nkv, int hd,
-                                         float scale, int window, int* status, void* stream) {
+                                         float scale, int window, int keep_first, const float* sinks, int* status,
+                                         void* stream) {
     DL_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill: bad sizes");
     DL_REQUIRE(scale > 0.f, "attention_prefill: the score scale must be positive");
+    DL_REQUIRE(keep_first >= 0 && window >= 0, "attention_prefill: the window and the kept first tokens cannot be negative");
     DL_REQUIRE(status != nullptr, "attention_prefill: needs a status word");
     DL_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)out % 4) == 0 &&
                    ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0,
@@ -378,7 +392,7 @@ extern "C" int dl_attention_prefill_bf16(const void* q, int q_stride, void* out,
 #define AP_CASE(HDV)                                                                                                  \
     if (hd == HDV)                                                                                                    \
         return ap_launch<HDV>(grid, s, q, q_stride, out, out_stride, k_pool, v_pool, n_pages, tile_seq, tile_row0,     \
-                              seq_start, seq_new, cu_new, block_table, bt_stride, nh, nkv, scale, window, status);
+                              seq_start, seq_new, cu_new, block_table, bt_stride, nh, nkv, scale, window, keep_first, sinks, status);
     AP_CASE(32) AP_CASE(64) AP_CASE(96) AP_CASE(128)
 #undef AP_CASE
     return dl_fail(DL_ERR_UNSUPPORTED, "attention_prefill: head_dim %d (takes 32, 64, 96, 128)", hd);

@@ -20,7 +20,7 @@ _library.register_signatures({
     "dl_attention_decode_gated_bf16": [_P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I,
                                        _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                  _F, _I, _P, _P],
+                                  _F, _I, _I, _P, _P, _P],
     "dl_attention_prefill_tc_bf16": [_P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                      _F, _I, _P, _P],
 })
@@ -136,14 +136,16 @@ def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_h
 
 
 def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads, head_dim,
-             scale, window, plan):
-    tc = PREFILL_TC and head_dim in PREFILL_TC_HEAD_DIMS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+             scale, window, plan, keep_first=0, sinks=None):
+    # kept first tokens and sinks are the mma.sync kernel's, at every head size
+    tc = PREFILL_TC and head_dim in PREFILL_TC_HEAD_DIMS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 \
+        and not keep_first and sinks is None
     rows = PREFILL_TC_ROWS if tc else PREFILL_ROWS
     if ("prefill_tiles", rows) not in plan.scratch:
         # tiles that see the most keys first: the kernels start blocks in this order, and the short
         # ones at the end fill the multiprocessors' last gaps
         tiles = [(b, r0) for b, n in enumerate(plan.news) for r0 in range(0, n, rows)]
-        tiles.sort(key=lambda t: -(plan.starts[t[0]] + min(plan.news[t[0]], t[1] + rows)))
+        tiles.sort(key=lambda t: -((plan.starts[t[0]] if plan.starts else 0) + min(plan.news[t[0]], t[1] + rows)))
         tile_seq, tile_row0 = [t[0] for t in tiles], [t[1] for t in tiles]
         host = torch.tensor(tile_seq + tile_row0, dtype=torch.int32).pin_memory()
         dev = host.to(q.device, non_blocking=True)
@@ -161,6 +163,7 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
                   n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], n_heads, n_kv_heads, head_dim, scale, window,
+                  int(keep_first), None if sinks is None else sinks.data_ptr(),
                   _library.status_word(q.device).data_ptr(), _library.current_stream())
     return True
 
@@ -168,17 +171,19 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
 def run(q, q_stride, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
         n_heads, n_kv_heads, head_dim, scale, window, plan, keep_first=0, sinks=None):
     """Run a tensor-core kernel into ``out`` and return True, or return False to let the
-    generic kernel take the call (kept first tokens and sinks are the generic kernel's)."""
-    if keep_first or sinks is not None:
-        return False
+    generic kernel take the call.  With kept first tokens or sinks every step, a decode step too, is the packed
+    mma.sync kernel's (a sequence's single token is a tile of one row; the window bounds what it reads)."""
     if q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16 or head_dim not in DECODE_HEAD_DIMS:
         return False
-    if plan.all_single and q.shape[0] == plan.n_seqs:
+    special = bool(keep_first) or sinks is not None
+    if special and (out.stride(0) % 2 or out.data_ptr() % 4):
+        return False
+    if not special and plan.all_single and q.shape[0] == plan.n_seqs:
         if n_heads // n_kv_heads > 16 or not decode_fits(n_heads // n_kv_heads, head_dim):
             return False
         return _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads,
                        head_dim, scale, window, plan)
     if plan.news and q.shape[0] == sum(plan.news):
         return _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads,
-                        head_dim, scale, window, plan)
+                        head_dim, scale, window, plan, keep_first, sinks)
     return False

@@ -216,27 +216,30 @@ def test_configurations_drawn_at_random(cpu_kernels, tmp_path):
 
 def test_a_window_that_is_one_token_off_would_show(cpu_kernels, tmp_path):
     """One attention layer sharpened until single keys decide rows: the plain implementation with a window one token
-    longer or shorter, with one kept token more or fewer, or without the sink differs visibly; the engine agrees with the
-    right one across a cut and through decoded tokens."""
-    folder = tz.sharp_folder(tmp_path, sink=4.0)
-    cfg, w = tz.read_folder(folder)
-    model = load_into(DecoderModel(build_spec(load_config(folder)), CPU), folder)
-    tokens = tz.random_tokens(90, cfg["vocab"], 4)
-    ref = pz.forward(cfg, w, tokens).float()
+    longer or shorter, or with one kept token more or fewer, differs visibly; with scores of order one, so does the one
+    without the sink.  The engine agrees with the right one across a cut and through decoded tokens."""
+    for sink, gains in ((20.0, 2.0), (2.0, 0.25)):
+        folder = tz.sharp_folder(tmp_path, sink=sink, gains=gains)
+        cfg, w = tz.read_folder(folder)
+        model = load_into(DecoderModel(build_spec(load_config(folder)), CPU), folder)
+        tokens = tz.random_tokens(90, cfg["vocab"], 4)
+        ref = pz.forward(cfg, w, tokens).float()
+        rms = ref.pow(2).mean(-1).sqrt()
 
-    def changed(**mask):
-        other = copy.deepcopy(cfg)
-        other["layers"][0]["mixer"]["mask"].update(mask)
-        return pz.forward(other, w, tokens).float()
+        def changed(**mask):
+            other = copy.deepcopy(cfg)
+            other["layers"][0]["mixer"]["mask"].update(mask)
+            return pz.forward(other, w, tokens).float()
 
-    for wrong in (changed(size=22), changed(size=24), changed(keep_first=2), changed(keep_first=4),
-                  pz.forward(cfg, dict(w, **{"l0.mix.sink": w["l0.mix.sink"] - 30.0}), tokens).float()):
-        assert float((wrong - ref).abs().max()) > 5e-3
-    cache = model.new_cache(256)
-    s = cache.open_sequence()
-    out = [run_step(model, cache, [StepEntry(s, tokens[:70], list(range(70)))])]
-    out += [run_step(model, cache, [StepEntry(s, [t])]) for t in tokens[70:]]
-    assert torch.allclose(torch.cat(out), ref, atol=3e-4)
+        controls = [changed(size=22), changed(size=24), changed(keep_first=2), changed(keep_first=4)] if gains > 1 else \
+            [pz.forward(cfg, dict(w, **{"l0.mix.sink": w["l0.mix.sink"] - 30.0}), tokens).float()]
+        for wrong in controls:
+            assert int(((wrong - ref).pow(2).mean(-1).sqrt() / rms > 1e-2).sum()) >= 5
+        cache = model.new_cache(256)
+        s = cache.open_sequence()
+        out = [run_step(model, cache, [StepEntry(s, tokens[:70], list(range(70)))])]
+        out += [run_step(model, cache, [StepEntry(s, [t])]) for t in tokens[70:]]
+        assert float(((torch.cat(out) - ref).pow(2).mean(-1).sqrt() / rms).max()) < 1e-4
 
 
 def test_trace_replay_of_a_zemezen_folder(cpu_kernels, tmp_path):

@@ -63,7 +63,8 @@ def load_pair(tmp, which, dtype, seed=0):
     from dotllm_b200 import Model
     key = (which, dtype, seed)
     if key not in _loaded:
-        folder = tz.sharp_folder(tmp, dtype=dtype, seed=seed, sink=4.0) if which == "sharp" else \
+        folder = tz.sharp_folder(tmp, dtype=dtype, seed=seed, sink=20.0) if which == "sharp" else \
+            tz.sharp_folder(tmp, dtype=dtype, seed=seed, sink=2.0, gains=0.25) if which == "soft" else \
             tz.make_folder(tmp, which, seed=seed, dtype=dtype)
         cfg, weights = tz.read_folder(folder)
         _loaded[key] = (Model.load(folder, dtype=dtype), cfg, weights, folder)
@@ -352,27 +353,29 @@ def test_keys_at_the_windows_edges_decide_whole_rows(tmp):
     when the sink is taken away; the engine must agree with the right one: in a prompt that crosses pages, across a
     portion's start, and when decoding goes on over page borders while the window gives pages back."""
     dtype = torch.float32
-    model, cfg, w, _ = load_pair(tmp, "sharp", dtype)
-    tokens = tz.random_tokens(330, cfg["vocab"], 3)
-    ref = pz.forward(cfg, w, tokens)
-    rms = ref.pow(2).mean(-1).sqrt()
+    tokens = tz.random_tokens(330, 120, 3)
+    for which in ("sharp", "soft"):
+        model, cfg, w, _ = load_pair(tmp, which, dtype)
+        ref = pz.forward(cfg, w, tokens)
+        rms = ref.pow(2).mean(-1).sqrt()
 
-    def changed(**mask):
-        other = copy.deepcopy(cfg)
-        other["layers"][0]["mixer"]["mask"].update(mask)
-        return pz.forward(other, w, tokens)
+        def changed(**mask):
+            other = copy.deepcopy(cfg)
+            other["layers"][0]["mixer"]["mask"].update(mask)
+            return pz.forward(other, w, tokens)
 
-    for wrong in (changed(size=22), changed(size=24), changed(keep_first=2), changed(keep_first=4),
-                  pz.forward(cfg, dict(w, **{"l0.mix.sink": w["l0.mix.sink"] - 30.0}), tokens)):
-        assert int(((wrong - ref).pow(2).mean(-1).sqrt() / rms > 1e-2).sum()) >= 20
-    for cuts in ([330], [63, 1, 1, 200], [128, 64, 2], [290], [20]):
-        got = run_cuts(model, tokens, cuts)
-        assert rel_err(got, ref) < 1e-4, cuts
-    bf = load_pair(tmp, "sharp", torch.bfloat16)
-    ref16 = pz.forward(bf[1], bf[2], tokens)
-    for cuts in ([300], [100]):
-        row_err = row_errors(run_cuts(bf[0], tokens, cuts), ref16)
-        assert float(row_err.median()) < 3e-2 and int((row_err > 0.3).sum()) <= 3
+        controls = [changed(size=22), changed(size=24), changed(keep_first=2), changed(keep_first=4)] if which == "sharp" else \
+            [pz.forward(cfg, dict(w, **{"l0.mix.sink": w["l0.mix.sink"] - 30.0}), tokens)]       # with scores of order one the sink shows
+        for wrong in controls:
+            assert int(((wrong - ref).pow(2).mean(-1).sqrt() / rms > 1e-2).sum()) >= 20
+        for cuts in ([330], [63, 1, 1, 200], [128, 64, 2], [290], [20]):
+            got = run_cuts(model, tokens, cuts)
+            assert rel_err(got, ref) < 1e-4, cuts
+        bf = load_pair(tmp, which, torch.bfloat16)
+        ref16 = pz.forward(bf[1], bf[2], tokens)
+        for cuts in ([300], [100]):
+            row_err = row_errors(run_cuts(bf[0], tokens, cuts), ref16)
+            assert float(row_err.median()) < 4e-2 and int((row_err > 0.3).sum()) <= 6, (which, cuts, float(row_err.median()), int((row_err > 0.3).sum()))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

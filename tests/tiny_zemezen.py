@@ -184,12 +184,13 @@ def rescale(folder, factors):
     return folder
 
 
-def sharp_folder(tmp_path, dtype=torch.float32, seed=0, sink=None):
+def sharp_folder(tmp_path, dtype=torch.float32, seed=0, sink=None, gains=2.0):
     """A folder of the sharp configuration whose query and key norms' gains are scaled up (the norms undo any scale on
     the projections), so that with the configuration's large score scale a query's softmax all but picks one key;
-    ``sink`` sets every head's sink."""
-    folder = make_folder(tmp_path, "sharp", seed=seed, dtype=dtype)
-    rescale(folder, {"l0.mix.q.norm": 4.0, "l0.mix.k.norm": 4.0})
+    ``sink`` sets every head's sink.  With ``gains`` 0.25 the scores stay of order one instead, and a sink of that order
+    takes a visible share of every row's softmax."""
+    folder = make_folder(tmp_path / f"gains{gains}_sink{sink}", "sharp", seed=seed, dtype=dtype)
+    rescale(folder, {"l0.mix.q.norm": gains, "l0.mix.k.norm": gains, "l0.mix.o": 16.0})       # and the mixer outweighs the embedding
     if sink is not None:
         from dotllm_b200.weights.safetensors_io import SafetensorsFile, save_safetensors
         path = folder / "model.safetensors"
