@@ -7,6 +7,7 @@
     python bench.py --workload short-prompts          # time to the first token of single short prompts, eager and captured
     python bench.py --workload kubedra [--shape 1b]   # the Kubedra design beside a Llama of equal width and depth, and its kernels
     python bench.py --workload komulorn [--shape 1b]  # the Komulorn design beside a Llama of equal width, heads and depth, and its kernels
+    python bench.py --workload zemezen [--shape 1b]   # the Zemezen design beside a Kubedra of equal width and depth, and its kernels
     python bench.py --impl plain-cpu                  # the plain implementation under tests/, timed on the CPU
 
 A "step" is one decode step: one new token for each of ``batch`` sequences that already hold
@@ -128,13 +129,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--repeats", type=int, default=5, help="repetitions of every timed region (best and CV are reported)")
-    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts", "kubedra", "komulorn"],
+    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts", "kubedra", "komulorn", "zemezen"],
                     help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps; "
                          "staggered: Model.generate on 64 prompts whose requests end five steps apart; "
                          "short-prompts: the time to the first token of single prompts of 20 to 1,024 tokens; "
                          "kubedra: prefill and decode of the Kubedra design at layer sizes of a real model beside a Llama of "
                          "equal width and depth, and each of its kernels against its roofline; "
-                         "komulorn: the same for the Komulorn design beside a Llama of equal width, heads and depth")
+                         "komulorn: the same for the Komulorn design beside a Llama of equal width, heads and depth; "
+                         "zemezen: the same for the Zemezen design beside a Kubedra of equal width and depth")
     ap.add_argument("--no-generate", action="store_true", help="skip the Model.generate cells")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -168,6 +170,8 @@ def main():
         return kubedra_workload(args)
     if args.workload == "komulorn":
         return komulorn_workload(args)
+    if args.workload == "zemezen":
+        return zemezen_workload(args)
     pk = peaks()
     shape_name, shape = SHAPES[args.shape]
     cfg_dict = dict(shape, num_hidden_layers=args.layers or shape["num_hidden_layers"])
@@ -751,6 +755,142 @@ def komulorn_workload(args):
                       "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16",
                       "data": "synthetic", "vs_baseline": None, "clocks": sampler.stop(),
                       "config": {"model": "Komulorn, four layers at the sizes named", "batch": 8, "context": ctx, "prefill_tokens": T,
+                                 "l2": "flushed between a kernel's timed launches"},
+                      "peaks": pk, "sizes": out}))
+    return 0
+
+
+ZEMEZEN_SIZES = {
+    # width, heads and feed-forward of the Llama shape of the same name, state and latent sizes of the Kubedra sizes above; four
+    # layers: delta rule + dense, delta rule + experts, latent attention + experts, windowed attention + dense
+    "1b": dict(width=2048, heads=16, key=64, value=128, conv=4, kv_rank=128, att_dim=128, att_heads=16, att_kv=4, window=1024,
+               keep=4, rot=64, ff=8192, experts=16, top=2, groups=(4, 2), expert_ff=2048),
+    "8b": dict(width=4096, heads=32, key=64, value=128, conv=4, kv_rank=128, att_dim=128, att_heads=32, att_kv=8, window=1024,
+               keep=4, rot=64, ff=14336, experts=32, top=4, groups=(8, 4), expert_ff=2048),
+}
+
+
+def zemezen_workload(args):
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 at context 2,048) tokens per second of a four-layer
+    Zemezen model at a real model's layer sizes, beside a four-layer Kubedra (the closest design here: a recurrent state
+    per head, latent attention, routed experts) of the same width, heads, state, latent, window and feed-forward sizes;
+    then every kernel the design added, alone, against its roofline, beside the like kernel of the Kubedra or Llama path.
+    Random weights, synthetic tokens, bfloat16, CUDA events, an L2 flush between the timed launches of a kernel."""
+    import numpy as np
+    import torch
+    from dotllm_b200 import Model
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.engine.step import AttentionPlan
+    from dotllm_b200.kernels import ops
+    tools = design_bench_tools(args)
+    pk, hbm, tflops, dev, T, ctx, sampler, timed, model_points = (tools.pk, tools.hbm, tools.tflops, tools.dev, tools.T, tools.ctx,
+                                                                  tools.sampler, tools.timed, tools.model_points)
+    sizes = ["1b", "8b"] if args.shape not in ("1b",) else ["1b"]
+
+    def kernel_table(z):
+        W, H, dk, dv, K, E, top = z["width"], z["heads"], z["key"], z["value"], z["conv"], z["experts"], z["top"]
+        nh, nkv, hd, window, keep = z["att_heads"], z["att_kv"], z["att_dim"], z["window"], z["keep"]
+        bf = torch.bfloat16
+        rows = {}
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+
+        def row(name, fn, bytes_=0, flops=0):
+            us = timed(fn) * 1000.0
+            need = max(bytes_ / hbm, flops / tflops) * 1e6
+            rows[name] = {"us": round(us, 1), "roofline_us": round(need, 2), "frac": round(need / us, 4)}
+        for label, n, n_seqs in (("prefill", T, 1), ("decode", 64, 64)):
+            # the delta rule (convolutions, unit lengths, decays, the recurrence) beside the gated-linear-attention scan
+            kw, vw = H * dk, H * dv
+            C = 2 * kw + vw
+            proj = torch.randn(n, C + H, device=dev).to(bf)
+            taps = (torch.randn(C, K, device=dev) * 0.5).to(bf)
+            zz, zb, a_log = torch.randn(n, kw, device=dev), torch.zeros(kw, device=dev), torch.zeros(H, device=dev)
+            memory = torch.zeros(n_seqs + 1, H * dk * dv + (K - 1) * C, device=dev)
+            cu = torch.arange(0, n + 1, n // n_seqs, dtype=torch.int32, device=dev)
+            seq = torch.arange(n, dtype=torch.int32, device=dev) // (n // n_seqs)
+            slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+            delta = lambda: ops.delta_rule(proj, taps, proj[:, C:], zz, zb, a_log, seq, cu, slots, memory, H, H, dk, dv, dk ** -0.5, 1e-6)
+            io = n * (C * 2 + kw * 4 + vw * 4) + 2 * n_seqs * H * dk * dv * 4
+            row(f"delta_rule (prepare + scan) {label}", delta, bytes_=io, flops=6 * n * H * dk * dv)
+            state = torch.zeros(n_seqs + 1, H, dk, dv, device=dev)
+            gla = lambda: ops.gla_scan(proj[:, :kw], proj[:, kw:2 * kw], proj[:, 2 * kw:2 * kw + vw], zz, zb, cu, slots, state,
+                                       H, dk, dv, dk ** -0.5, 16.0)
+            row(f"kubedra gla_scan {label}", gla, bytes_=n * (C * 2 + kw * 4 + vw * 4) + 2 * n_seqs * H * dk * dv * 4, flops=4 * n * H * dk * dv)
+            o = gla()
+            g = torch.randn(n, vw, device=dev).to(bf)
+            for gate in ("sigmoid", "silu"):
+                row(f"head_norm_gate {gate} {label}", lambda: ops.head_norm_gate(o, g, torch.ones(dv, device=dev), H, dv, 1e-5, bf, gate=gate),
+                    bytes_=n * vw * (4 + 2 + 2))
+            # queries and keys normalised per head; windowed attention with kept tokens and sinks beside the same window without
+            qk = torch.randn(n, (nh + 2 * nkv) * hd, device=dev).to(bf)
+            gq = torch.ones(hd, device=dev)
+            row(f"head_rmsnorm (queries and keys) {label}", lambda: ops.head_rmsnorm(qk[:, :(nh + nkv) * hd], gq, nh, hd, 1e-5, gq, nkv),
+                bytes_=n * (nh + nkv) * hd * 4)
+            per = ctx if label == "decode" else n
+            pages = (per + 63) // 64
+            k_pool = torch.randn(n_seqs * pages + 1, nkv, 64, hd, device=dev).to(bf)
+            v_pool = torch.randn(n_seqs * pages + 1, nkv, hd, 64, device=dev).to(bf)
+            table = torch.arange(n_seqs * pages, dtype=torch.int32, device=dev).reshape(n_seqs, pages)
+            starts, news = ([0], [n]) if label == "prefill" else ([ctx - 1] * n_seqs, [1] * n_seqs)
+            totals = [a + b for a, b in zip(starts, news)]
+            pos = i32([a + i for a, b in zip(starts, news) for i in range(b)])
+            q = qk[:, :nh * hd]
+            sinks = torch.zeros(nh, device=dev)
+            seen = sum(min(p + 1, window + keep) for p in pos.tolist())             # keys the step's queries see, per KV head
+            att_bytes = (min(per, window + 64) * n_seqs if label == "decode" else per) * nkv * hd * 2 * 2 + n * nh * hd * 4
+            for name, kw_ in (("windowed attention, kept tokens and sinks", dict(keep_first=keep, sinks=sinks)), ("llama windowed attention", {})):
+                plan = AttentionPlan(n_seqs, max(news), max(totals), label == "decode", i32(starts), i32(news),
+                                     i32([0] + list(np.cumsum(news))), i32(totals), list(starts), list(news))
+                row(f"{name} {label}", lambda: ops.attention(q, k_pool, v_pool, seq, pos, table, nh, nkv, hd, hd ** -0.5, window, plan=plan, **kw_),
+                    bytes_=att_bytes, flops=4 * seen * nh * hd)
+            del k_pool, v_pool
+            # the router: softmax over all experts and groups, beside the softmax over the chosen
+            x = torch.randn(n, W, device=dev).to(bf)
+            wr = torch.randn(E, W, device=dev).to(bf)
+            row(f"route_topk, softmax over all, groups {label}", lambda: ops.route_topk(x, wr, None, top, scoring="softmax_all", groups=z["groups"]),
+                bytes_=n * W * 2 + E * W * 2, flops=2 * n * E * W)
+            row(f"kubedra route_topk {label}", lambda: ops.route_topk(x, wr, None, top), bytes_=n * W * 2 + E * W * 2, flops=2 * n * E * W)
+        return rows
+
+    out = {}
+    for name in sizes:
+        z = ZEMEZEN_SIZES[name]
+        vocab = 32000
+        moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+               "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+        dense = {"kind": "dense", "ff": z["ff"]}
+        mix_d = {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["key"], "vdim": z["value"], "conv": z["conv"], "ranks": [64, 64]}
+        mix_l = {"heads": z["heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "kv_rank": z["kv_rank"], "scale": z["att_dim"] ** -0.5}
+        mix_a = {"heads": z["att_heads"], "kv_heads": z["att_kv"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5,
+                 "mask": {"size": z["window"], "keep_first": z["keep"]}, "rot": {"dims": z["rot"], "base": 10000.0}}
+        zcfg = {"architecture": "Zemezen", "vocab": vocab, "width": z["width"], "max_positions": 8192, "norm": {"eps": 1e-5},
+                "layers": [{"type": "channel_delta", "mixer": mix_d, "mlp": dense}, {"type": "channel_delta", "mixer": mix_d, "mlp": moe},
+                           {"type": "latent_attention", "mixer": mix_l, "mlp": moe}, {"type": "attention", "mixer": mix_a, "mlp": dense}]}
+        kz = KUBEDRA_SIZES[name]
+        mix_g = {"heads": kz["heads"], "dim": kz["key"], "vdim": kz["value"], "tau": 16.0, "decay_rank": 64}
+        mix_kl = {"heads": kz["heads"], "dim": kz["att_dim"], "vdim": kz["att_dim"], "q_rank": kz["q_rank"], "kv_rank": kz["kv_rank"],
+                  "mask": {"size": kz["window"]}}
+        kmoe = {"kind": "moe", "expert": {"ff": kz["expert_ff"], "limit": 7.0}, "router": {"experts": kz["experts"], "top": kz["top"]}}
+        kcfg = {"architecture": "Kubedra", "vocab": vocab, "width": kz["width"], "max_positions": 8192, "norm": {"eps": 1e-5},
+                "layers": [{"type": "gla", "mixer": mix_g, "mlp": dense}, {"type": "gla", "mixer": mix_g, "mlp": kmoe},
+                           {"type": "latent_attention", "mixer": mix_kl, "mlp": kmoe},
+                           {"type": "latent_attention", "mixer": mix_kl, "mlp": dense}]}
+        point = {}
+        for label, cfg_dict in (("zemezen", zcfg), ("kubedra", kcfg)):
+            model = Model.random(config_from_dict(cfg_dict), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+            point[label] = model_points(model, vocab)
+            print(f"[bench] {name} {label}: {point[label]}", file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        point["kernels"] = kernel_table(z)
+        for k, v in point["kernels"].items():
+            print(f"[bench] {name} {k}: {v}", file=sys.stderr, flush=True)
+        out[name] = point
+    first = out[sizes[0]]
+    print(json.dumps({"metric": "zemezen_decode_tokens_per_second", "value": first["zemezen"]["decode_b8_tok_s"], "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16",
+                      "data": "synthetic", "vs_baseline": None, "clocks": sampler.stop(),
+                      "config": {"model": "Zemezen, four layers at the sizes named", "batch": 8, "context": ctx, "prefill_tokens": T,
                                  "l2": "flushed between a kernel's timed launches"},
                       "peaks": pk, "sizes": out}))
     return 0
