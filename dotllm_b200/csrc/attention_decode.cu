@@ -123,10 +123,20 @@ __device__ __forceinline__ uint4 ad_lds128(uint32_t addr) {
 // Pages of a sequence that its newest token sees (from the page of the first visible key).  A length
 // of 0 marks a row that holds nothing (an idle row of a captured step wider than its batch): it has
 // no pages, so no block walks it, nothing is read or written for it and its output row stays as it was.
+//
+// A window may keep a sequence's first `keep` keys visible after it has passed them.  The visible pages are then the
+// kept pages that lie wholly before the window's first page, followed by the window's pages: visible page v of the
+// list is page v of the sequence while v < kept, and page first + (v - kept) from there on.
+struct AdWin {
+    int size, keep;          // keys in the window (0: all), first keys that stay visible
+};
 __device__ __forceinline__ int ad_first_key(int len, int window) { return (window > 0 && len - window > 0) ? len - window : 0; }
-__device__ __forceinline__ int ad_pages_of(int len, int window) {
+__device__ __forceinline__ int ad_kept_pages(int len, AdWin win) {
+    return min((win.keep + DL_PAGE - 1) / DL_PAGE, ad_first_key(len, win.size) / DL_PAGE);
+}
+__device__ __forceinline__ int ad_pages_of(int len, AdWin win) {
     if (len <= 0) return 0;
-    return (len - 1) / DL_PAGE - ad_first_key(len, window) / DL_PAGE + 1;
+    return (len - 1) / DL_PAGE - ad_first_key(len, win.size) / DL_PAGE + 1 + ad_kept_pages(len, win);
 }
 
 // The work of a step is the list of all visible pages, ordered by (sequence, KV head, page), cut into
@@ -135,7 +145,7 @@ struct AdCut {
     int total, share;        // pages in the step, pages per block
 };
 
-__device__ __forceinline__ AdCut ad_cut(const int32_t* seq_len, int n_seqs, int nkv, int window, int n_blocks, int lane) {
+__device__ __forceinline__ AdCut ad_cut(const int32_t* seq_len, int n_seqs, int nkv, AdWin window, int n_blocks, int lane) {
     int sum = 0;
     for (int b0 = 0; b0 < n_seqs; b0 += 32)
         if (b0 + lane < n_seqs) sum += ad_pages_of(seq_len[b0 + lane], window);
@@ -148,7 +158,7 @@ __device__ __forceinline__ AdCut ad_cut(const int32_t* seq_len, int n_seqs, int 
 }
 
 // The sequence that holds page r of the list (r < total), and the pages of the list before it.
-__device__ __forceinline__ void ad_locate(const int32_t* seq_len, int n_seqs, int nkv, int window, int r, int lane,
+__device__ __forceinline__ void ad_locate(const int32_t* seq_len, int n_seqs, int nkv, AdWin window, int r, int lane,
                                           int* b_out, int* before_out) {
     int before = 0, b = n_seqs, b_before = 0;
     for (int b0 = 0; b0 < n_seqs; b0 += 32) {
@@ -180,12 +190,13 @@ struct AdWalk {
     bool first;              // the next segment is the block's first
 };
 struct AdSeg {
-    int b, kvh, len, first_key, run_begin, page0, n_pages, slot;
+    int b, kvh, len, first_key, n_pages, slot;
+    int vis0, kept, first_page;      // the segment's first page in the pair's visible list; kept pages of the list; the window's first page
     int pair_begin, pair_pages;      // where the (sequence, KV head)'s pages start in the step's list, and how many they are
     bool whole;
 };
 
-__device__ __forceinline__ AdWalk ad_walk_begin(const AdCut& c, const int32_t* seq_len, int n_seqs, int nkv, int window,
+__device__ __forceinline__ AdWalk ad_walk_begin(const AdCut& c, const int32_t* seq_len, int n_seqs, int nkv, AdWin window,
                                                 int block, int lane) {
     AdWalk w;
     w.r = min(c.total, block * c.share);
@@ -209,16 +220,23 @@ __device__ __forceinline__ AdWalk ad_walk_begin(const AdCut& c, const int32_t* s
     return w;
 }
 
+// Page i of a segment, as a page of its sequence.
+__device__ __forceinline__ int ad_seg_page(const AdSeg& s, int i) {
+    const int v = s.vis0 + i;
+    return v < s.kept ? v : s.first_page + (v - s.kept);
+}
+
 // The next segment of the walk; false when the share is used up.
-__device__ __forceinline__ bool ad_walk_next(AdWalk& w, AdSeg& s, const int32_t* seq_len, int n_seqs, int nkv, int window) {
+__device__ __forceinline__ bool ad_walk_next(AdWalk& w, AdSeg& s, const int32_t* seq_len, int n_seqs, int nkv, AdWin window) {
     if (w.r >= w.r_end || w.b >= n_seqs) return false;
     const int n = min(w.np - w.pg, w.r_end - w.r);
     s.b = w.b;
     s.kvh = w.kvh;
     s.len = w.len;
-    s.first_key = ad_first_key(w.len, window);
-    s.page0 = s.first_key / DL_PAGE + w.pg;
-    s.run_begin = s.page0 * DL_PAGE;
+    s.first_key = ad_first_key(w.len, window.size);
+    s.first_page = s.first_key / DL_PAGE;
+    s.kept = ad_kept_pages(w.len, window);
+    s.vis0 = w.pg;
     s.n_pages = n;
     s.whole = (w.pg == 0 && n == w.np);
     s.pair_begin = w.r - w.pg;
@@ -259,6 +277,9 @@ struct AdFresh {
     const float* v_bias;
     const __nv_bfloat16* gate;       // one logit per (sequence, query head), rows gate_stride apart, or NULL: a head's output
     int gate_stride;                 // is multiplied by sigmoid(logit) as it is written
+    // two options of the mask and of the softmax that travel with the others
+    int keep_first;                  // with a window: the sequence's first keys that stay visible behind it
+    const float* sinks;              // [nh] float32 or NULL: one more term exp(sinks[head]) in the head's denominator, no key, no value
 };
 
 // The same roundings as the rope kernels (no contraction), so that the fused and the separate way
@@ -306,6 +327,11 @@ __device__ __forceinline__ void ad_add8(uint4& x, const float* bias) {
     for (int e = 0; e < 8; ++e) a[e] = __float2bfloat16_rn(__bfloat162float(a[e]) + bias[e]);
 }
 
+// The sink's term of a head's denominator, in units of the running maximum m (base 2): exp(sink) / 2^m.
+__device__ __forceinline__ float ad_sink_term(const float* sinks, int head, float m) {
+    return sinks == nullptr ? 0.f : ad_ex2(sinks[head] * 1.4426950408889634f - m);
+}
+
 __device__ __forceinline__ float ad_gate_factor(const __nv_bfloat16* gate_row, int head) {
     return gate_row == nullptr ? 1.f : 1.f / (1.f + expf(-__bfloat162float(gate_row[head])));
 }
@@ -318,7 +344,8 @@ __device__ __forceinline__ float ad_gate_factor(const __nv_bfloat16* gate_row, i
 template <int HD, int BATCH>
 __device__ __forceinline__ void ad_merge_pair(__nv_bfloat16* __restrict__ out_pair, int group, int i0, int n_seg, int slot_first,
                                               const float* __restrict__ part_o, const float* __restrict__ part_ml, int tid,
-                                              int n_threads, const __nv_bfloat16* __restrict__ gate_pair) {
+                                              int n_threads, const __nv_bfloat16* __restrict__ gate_pair,
+                                              const float* __restrict__ sinks_pair) {
     constexpr int hd4 = HD / 4;
     for (int idx = tid; idx < group * hd4; idx += n_threads) {
         const int r = idx / hd4, d = (idx - r * hd4) * 4;
@@ -351,6 +378,7 @@ __device__ __forceinline__ void ad_merge_pair(__nv_bfloat16* __restrict__ out_pa
                 }
             }
         }
+        l += ad_sink_term(sinks_pair, r, m);
         const float inv = (1.f / l) * ad_gate_factor(gate_pair, r);
         __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
         __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -368,7 +396,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         int out_stride, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, int n_pages,
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_table,
-                        int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int n_stages, int n_ring,
+                        int bt_stride, int n_seqs, int nh, int nkv, float scale, int window_size, int n_stages, int n_ring,
                         float* __restrict__ part_o,
                         float* __restrict__ part_ml, int* __restrict__ pair_counters, const AdFresh fresh,
                         int* __restrict__ status) {
@@ -389,6 +417,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const AdWin window = {window_size, window_size > 0 ? fresh.keep_first : 0};
     // The kernel checks its own shared-memory layout: if the launch gave it less dynamic shared
     // memory than the stages and merge buffers need, it records status 11 and touches nothing.
     uint32_t smem_bytes;
@@ -427,9 +456,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         AdWalk walk = ad_walk_begin(cut, seq_len, n_seqs, nkv, window, blockIdx.x, lane);
         AdSeg w;
         while (!stop && ad_walk_next(walk, w, seq_len, n_seqs, nkv, window)) {
-            const int32_t* pages = block_table + (size_t)w.b * bt_stride + w.page0;
+            const int32_t* pages = block_table + (size_t)w.b * bt_stride;
             for (int i0 = 0; i0 < w.n_pages && !stop; i0 += 32) {
-                const int mine = (i0 + lane < w.n_pages) ? pages[i0 + lane] : 0;
+                const int mine = (i0 + lane < w.n_pages) ? pages[ad_seg_page(w, i0 + lane)] : 0;
                 const int count = min(32, w.n_pages - i0);
                 for (int j = 0; j < count; ++j, ++n) {
                     const int page = __shfl_sync(0xffffffffu, mine, j);
@@ -441,7 +470,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         } else if (n >= n_ring && !ad_mbar_wait(&empty_bar[s], ((n / n_ring) - 1) & 1, &gave_up)) {
                             bad = 1;
                         } else {
-                            if (!waited && fresh.k == nullptr && w.page0 + i0 + j == (w.len - 1) / DL_PAGE) {
+                            if (!waited && fresh.k == nullptr && ad_seg_page(w, i0 + j) == (w.len - 1) / DL_PAGE) {
                                 dl_grid_dependency_wait();
                                 waited = true;
                             }
@@ -526,7 +555,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
             const int i_first = ((warp - n0) % n_stages + n_stages) % n_stages;   // first i with (n0 + i) % n_stages == warp
             // The warp that will meet the page of the step's own token asks for that token's key, value
             // and table rows now, so that they are in registers when the page arrives.
-            const int i_new = fresh.k != nullptr ? (w.len - 1) / DL_PAGE - w.page0 : -1;
+            const int i_new = fresh.k != nullptr ? w.pair_pages - 1 - w.vis0 : -1;      // the newest page is the list's last
             const bool mine_new = i_new >= 0 && i_new < w.n_pages && (n0 + i_new) % n_stages == warp;
             uint2 kn_lo = make_uint2(0u, 0u), kn_hi = make_uint2(0u, 0u);
             float4 kn_c = make_float4(1.f, 1.f, 1.f, 1.f), kn_s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -564,10 +593,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     gave_up = 1;
                     continue;                                 // keep walking so that every barrier below is reached
                 }
-                const int base = w.run_begin + i * DL_PAGE;  // first key of the page
+                const int base = ad_seg_page(w, i) * DL_PAGE;  // first key of the page
                 __nv_bfloat16* kp = stage_mem + (size_t)s * 2 * PAGE_ELEMS;
                 __nv_bfloat16* vp = kp + PAGE_ELEMS;
-                const bool ragged = (base + DL_PAGE > w.len) || (base < w.first_key);
+                // keys [gap_lo, gap_hi) of the sequence are hidden: older than the window and not among the kept first ones
+                const int gap_lo = min(window.keep, w.first_key), gap_hi = w.first_key;
+                const bool ragged = (base + DL_PAGE > w.len) || (max(base, gap_lo) < min(base + DL_PAGE, gap_hi));
                 if (fresh.k != nullptr && base <= w.len - 1 && w.len - 1 < base + DL_PAGE) {
                     // The page of the step's own token: its slot is stale in the copy that arrived.  Put the
                     // (rotated) key and the value there, in the stage and in the cache.
@@ -615,14 +646,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                 if (ragged) {
                     // Keys outside [first, len) may hold anything (even NaN): make their values exact
                     // zeros in the stage once, so that the product below needs no special case.
-                    // The invalid keys are a run at the page's start (older than the window) and a run at
-                    // its end (beyond the sequence): each lane clears those runs in its rows of V, eight
-                    // keys (16 bytes) at a time where a run covers whole groups of eight.
-                    const int lo_end = min(DL_PAGE, max(0, w.first_key - base));       // keys [0, lo_end) are too old
+                    // The invalid keys are a run near the page's start (older than the window, behind the kept first
+                    // keys if the page has some) and a run at its end (beyond the sequence): each lane clears those
+                    // runs in its rows of V, eight keys (16 bytes) at a time where a run covers whole groups of eight.
+                    const int lo_begin = min(DL_PAGE, max(0, gap_lo - base));
+                    const int lo_end = min(DL_PAGE, max(0, gap_hi - base));             // keys [lo_begin, lo_end) are too old
                     const int hi_begin = max(0, min(DL_PAGE, w.len - base));             // keys [hi_begin, 64) do not exist yet
                     for (int d = lane; d < HD; d += 32) {
                         __nv_bfloat16* row = vp + d * DL_PAGE;
-                        for (int k = 0; k < lo_end; ++k) row[k] = __float2bfloat16_rn(0.f);
+                        for (int k = lo_begin; k < lo_end; ++k) row[k] = __float2bfloat16_rn(0.f);
                         int k = hi_begin;
                         for (; k < DL_PAGE && (k & 7); ++k) row[k] = __float2bfloat16_rn(0.f);
                         for (; k < DL_PAGE; k += 8) *reinterpret_cast<uint4*>(row + k) = make_uint4(0u, 0u, 0u, 0u);
@@ -681,7 +713,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int key = base + 32 * h + 8 * t + 2 * j + e;
-                                if (key < w.first_key || key >= w.len) {
+                                if ((key >= gap_lo && key < gap_hi) || key >= w.len) {
                                     sc[h][j][e] = -INFINITY;
                                     sc[h][j][2 + e] = -INFINITY;
                                 }
@@ -820,6 +852,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     }
                 }
                 if (w.whole) {
+                    l += ad_sink_term(fresh.sinks, w.kvh * group + r, m);
                     const float inv = (1.f / l) * ad_gate_factor(fresh.gate != nullptr ? fresh.gate + (size_t)w.b * fresh.gate_stride : nullptr,
                                                                  w.kvh * group + r);
                     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
@@ -856,7 +889,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                 if (last)
                     ad_merge_pair<HD, WIDE ? 4 : 8>(out + (size_t)w.b * out_stride + (size_t)w.kvh * group * HD, group, i0, i1 - i0 + 1,
                                       (w.pair_begin == i0 * cut.share) ? 0 : 1, part_o, part_ml, tid, 32 * n_stages,
-                                      fresh.gate != nullptr ? fresh.gate + (size_t)w.b * fresh.gate_stride + w.kvh * group : nullptr);
+                                      fresh.gate != nullptr ? fresh.gate + (size_t)w.b * fresh.gate_stride + w.kvh * group : nullptr,
+                                      fresh.sinks != nullptr ? fresh.sinks + w.kvh * group : nullptr);
             }
         }
     }
@@ -961,9 +995,13 @@ static int ad_dispatch(const void* q, int q_stride, void* out, int out_stride, v
 extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                         const void* v_pool, int n_pages, const int32_t* seq_len,
                                         const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv,
-                                        int hd, float scale, int window, int blocks, float* part_o, float* part_ml,
-                                        int part_slots, int* pair_counters, int n_counters, int* status, void* stream) {
+                                        int hd, float scale, int window, int keep_first, const float* sinks, int blocks,
+                                        float* part_o, float* part_ml, int part_slots, int* pair_counters, int n_counters,
+                                        int* status, void* stream) {
+    DL_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention_decode: kept first keys need a window");
     AdFresh none = {};
+    none.keep_first = keep_first;
+    none.sinks = sinks;
     return ad_dispatch(q, q_stride, out, out_stride, const_cast<void*>(k_pool), const_cast<void*>(v_pool), n_pages, seq_len,
                        block_table, bt_stride, n_seqs, nh, nkv, hd, scale, window, blocks, part_o, part_ml, part_slots,
                        pair_counters, n_counters, none, status, stream);

@@ -13,7 +13,7 @@ from . import library as _library
 
 _P, _I, _F = _library._P, _library._I, _library._F
 _library.register_signatures({
-    "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I,
+    "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I,
                                  _P, _P, _I, _P, _I, _P, _P],
     "dl_attention_decode_fresh_bf16": [_P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                        _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
@@ -31,6 +31,7 @@ PREFILL_TC_HEAD_DIMS = (64, 128)     # head sizes of the tcgen05 prefill kernel;
 PREFILL_TC = True        # False: always the mma.sync kernel (tests compare the two)
 
 DECODE_HEAD_DIMS = (32, 64, 96, 128)
+DECODE_SPECIAL = True    # False: decode steps with kept first tokens or sinks take the packed prefill kernel (tests compare the two)
 DECODE_BLOCKS = 0        # > 0: persistent blocks of the decode kernel (tuning and tests); 0: one per multiprocessor
 
 
@@ -41,7 +42,7 @@ def decode_fits(group, head_dim):
 
 
 def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads, head_dim,
-            scale, window, plan):
+            scale, window, plan, keep_first=0, sinks=None):
     B = plan.n_seqs
     group = n_heads // n_kv_heads
     part_o, part_ml, slots = _decode_scratch(plan, group, head_dim, q.device)
@@ -49,8 +50,8 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
     _library.call("dl_attention_decode_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
-                  scale, window, DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots,
-                  counters.data_ptr(), counters.numel(),
+                  scale, window, int(keep_first), None if sinks is None else sinks.data_ptr(), DECODE_BLOCKS,
+                  part_o.data_ptr(), part_ml.data_ptr(), slots, counters.data_ptr(), counters.numel(),
                   _library.status_word(q.device).data_ptr(), _library.current_stream())
     return True
 
@@ -171,18 +172,18 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
 def run(q, q_stride, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
         n_heads, n_kv_heads, head_dim, scale, window, plan, keep_first=0, sinks=None):
     """Run a tensor-core kernel into ``out`` and return True, or return False to let the
-    generic kernel take the call.  With kept first tokens or sinks every step, a decode step too, is the packed
-    mma.sync kernel's (a sequence's single token is a tile of one row; the window bounds what it reads)."""
+    generic kernel take the call.  Kept first tokens and sinks are taken by the decode kernel (the kept pages join the
+    step's list of pages; the sink's term enters where a head is normalised) and by the packed mma.sync prefill kernel."""
     if q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16 or head_dim not in DECODE_HEAD_DIMS:
         return False
     special = bool(keep_first) or sinks is not None
     if special and (out.stride(0) % 2 or out.data_ptr() % 4):
         return False
-    if not special and plan.all_single and q.shape[0] == plan.n_seqs:
+    if plan.all_single and q.shape[0] == plan.n_seqs and (DECODE_SPECIAL or not special):
         if n_heads // n_kv_heads > 16 or not decode_fits(n_heads // n_kv_heads, head_dim):
             return False
         return _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads,
-                       head_dim, scale, window, plan)
+                       head_dim, scale, window, plan, keep_first, sinks)
     if plan.news and q.shape[0] == sum(plan.news):
         return _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads,
                         head_dim, scale, window, plan, keep_first, sinks)

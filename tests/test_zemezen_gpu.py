@@ -254,6 +254,54 @@ def test_windowed_attention_with_kept_tokens_and_sinks_alone(nh, nkv, hd, window
             assert float((no_sink.cpu() - want).abs().max()) > 1e-3
 
 
+@pytest.mark.parametrize("blocks", [0, 1, 3, 7])
+@pytest.mark.parametrize("nh,nkv,hd,window,keep", [(8, 2, 64, 100, 3), (4, 4, 128, 64, 64), (12, 1, 32, 70, 130), (6, 2, 96, 129, 65),
+                                                  (4, 2, 64, 1, 1), (2, 1, 64, 640, 200)])
+def test_decode_steps_with_kept_tokens_and_sinks_over_cut_pages(nh, nkv, hd, window, keep, blocks, monkeypatch):
+    """One new token per sequence, in bfloat16, through the decode kernel that shares the step's pages out to its blocks:
+    sequences that end on a page's first and last place, shorter than the window, shorter than the kept tokens, and long
+    ones whose kept pages and window pages land in different blocks (few blocks make every pair a cut one).  The pages
+    between the kept ones and the window's are NaN.  The packed prompt kernel with tiles of one row gives the same."""
+    from dotllm_b200.engine.step import AttentionPlan
+    from dotllm_b200.kernels import attention_fast
+    dtype = torch.bfloat16
+    lens = [1000, 64, 65, 200, 129, 1, 3, 449]
+    k_pool, v_pool, table = paged(lens, nkv, hd, dtype, 5)
+    gen = torch.Generator().manual_seed(7)
+    for b, n in enumerate(lens):
+        for p in range((n + 63) // 64):
+            page = int(table[b, p])
+            k_pool[page] = torch.randn(nkv, 64, hd, generator=gen).to(dtype)
+            v_pool[page] = torch.randn(nkv, hd, 64, generator=gen).to(dtype)
+            first = max(0, n - window)
+            if (p + 1) * 64 <= first and p * 64 >= keep:              # wholly hidden: between the kept tokens and the window
+                k_pool[page], v_pool[page] = float("nan"), float("nan")
+            if (p + 1) * 64 > n:                                      # places that no token has reached yet
+                k_pool[page, :, n - p * 64:, :] = float("nan")
+                v_pool[page, :, :, n - p * 64:] = float("nan")
+    sinks = g64(nh, seed=11, scale=2.0).float()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    B = len(lens)
+    starts, news = [n - 1 for n in lens], [1] * B
+    seq, pos = torch.arange(B, dtype=torch.int32), torch.tensor(starts, dtype=torch.int32)
+    q = g64(B, nh * hd, seed=13).to(dtype)
+    scale = 0.2
+    clean_k, clean_v = torch.nan_to_num(k_pool.float(), nan=0.0).to(dtype), torch.nan_to_num(v_pool.float(), nan=0.0).to(dtype)
+    want = kernel_refs.attention(q, clean_k, clean_v, seq, pos, table, nh, nkv, hd, scale, window, keep_first=keep, sinks=sinks)
+    make_plan = lambda: AttentionPlan(B, 1, max(lens), True, i32(starts), i32(news), i32(list(range(B + 1))), i32(lens), list(starts), list(news))
+    args = (q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), seq.to(DEV), pos.to(DEV), table.to(DEV), nh, nkv, hd, scale, window)
+    monkeypatch.setattr(attention_fast, "DECODE_BLOCKS", blocks)
+    got = ops.attention(*args, plan=make_plan(), keep_first=keep, sinks=sinks.to(DEV))
+    close(got, want, dtype)
+    if blocks == 0:
+        monkeypatch.setattr(attention_fast, "DECODE_SPECIAL", False)
+        other = ops.attention(*args, plan=make_plan(), keep_first=keep, sinks=sinks.to(DEV))
+        close(other, want, dtype)
+        close(got, other.float(), dtype, tol16=1e-2)
+        no_keep = ops.attention(*args, plan=make_plan(), sinks=sinks.to(DEV))
+        assert float((no_keep.float().cpu() - want).abs().max()) > 1e-3
+
+
 # ------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("which", ["A", "B", "C", "D"])
