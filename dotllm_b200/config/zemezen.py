@@ -32,7 +32,8 @@ class DeltaMixerConfig:
     @classmethod
     def from_dict(cls, d, where):
         ranks = d.get("ranks")
-        return cls(_get(d, "heads", int, where), _get(d, "kv_heads", int, where), _get(d, "dim", int, where),
+        heads = _get(d, "heads", int, where)
+        return cls(heads, _get(d, "kv_heads", int, where, default=heads, required=False), _get(d, "dim", int, where),
                    _get(d, "vdim", int, where), _get(d, "conv", int, where),
                    (int(ranks[0]), int(ranks[1])) if ranks else None)
 
@@ -75,7 +76,7 @@ class AttentionMixerConfig:
     dim: int
     vdim: int                     # the values are the keys: equal to dim
     scale: float
-    window: int                   # mask.size
+    window: Optional[int]         # mask.size; None (no mask in the entry): every earlier key
     keep_first: int               # mask.keep_first
     rot_dims: int
     rot_base: float
@@ -86,20 +87,24 @@ class AttentionMixerConfig:
         dim = _get(d, "dim", int, where)
         return cls(_get(d, "heads", int, where), _get(d, "kv_heads", int, where), dim,
                    _get(d, "vdim", int, where, default=dim, required=False), _get(d, "scale", float, where),
-                   _get(mask, "size", int, where + ".mask"), _get(mask, "keep_first", int, where + ".mask", default=0, required=False),
-                   _get(rot, "dims", int, where + ".rot"), _get(rot, "base", float, where + ".rot"))
+                   _get(mask, "size", int, where + ".mask", required=mask is not None),
+                   _get(mask, "keep_first", int, where + ".mask", default=0, required=False),
+                   _get(rot, "dims", int, where + ".rot", default=0, required=rot is not None),
+                   _get(rot, "base", float, where + ".rot", default=10000.0, required=rot is not None))
 
     def to_dict(self):
-        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-                "mask": {"size": self.window, "keep_first": self.keep_first},
-                "rot": {"dims": self.rot_dims, "base": self.rot_base}}
+        out = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale}
+        if self.window is not None:
+            out["mask"] = {"size": self.window, "keep_first": self.keep_first}
+        out["rot"] = {"dims": self.rot_dims, "base": self.rot_base}
+        return out
 
     def check(self, where):
         if min(self.heads, self.kv_heads, self.dim) <= 0 or self.heads % self.kv_heads:
             raise ConfigError(f"config.json: {where}: sizes must be positive and heads a multiple of kv_heads")
         if self.vdim != self.dim:
             raise ConfigError(f"config.json: {where}: the values are the keys, so vdim {self.vdim} must equal dim {self.dim}")
-        if self.window < 1 or self.keep_first < 0:
+        if (self.window is not None and self.window < 1) or self.keep_first < 0 or (self.keep_first and self.window is None):
             raise ConfigError(f"config.json: {where}.mask: a window holds at least the token itself, keep_first is not negative")
         if self.rot_dims < 0 or self.rot_dims % 2 or self.rot_dims > self.dim or self.rot_base <= 0:
             raise ConfigError(f"config.json: {where}.rot: dims must be even and at most dim, base positive")

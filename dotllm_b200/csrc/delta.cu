@@ -18,20 +18,21 @@
 // sequence was cut into steps.
 //
 // The scan: columns of S never mix, so a block owns DR_COLS value channels of one (sequence, head).  DR_SPLIT
-// lanes of one warp share a column, each with a run of ROWS key channels in registers; per token they decay their
-// rows, take the partial sums of S^T k, S^T q and q . k in one pass, exchange them by shuffles inside the warp
-// (no block barrier per token), and write the correction: o_t = (gS)^T q + (q . k) u, the same number as the read
-// after the write.  Tokens are staged in shared memory a batch at a time from registers that were loaded while
-// the batch before was walked.
+// lanes of one warp share a column, each with a run of ROWS key channels in registers; per token they take the
+// partial sums of S^T (g k), exchange them by shuffles inside the warp (no block barrier per token), write the decayed
+// rows plus the correction, and read the new rows with q.  Tokens are staged in shared memory a batch at a time from
+// registers that were loaded while the batch before was walked.
 #include "common.cuh"
 
 #define DP_THREADS 128
 
 __device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// One block per token.  x: the stacked projection's rows (q channels, then k, then v: C = 2*G*dim + H*vdim columns from
-// column 0 of `x`, rows `ld` apart); taps [C, K] of x's type; history: float32 [K - 1, C] per slot at `hist` +
-// slot * slot_stride.  Row t is token (t - cu_new[b]) of sequence b = token_seq[t].
+// One block per (run of tokens, part): the parts are the G query heads, the G key heads and the H value heads of a token, so
+// that a step of few tokens still fills the machine; a step of many tokens gives a block `per_block` of them in a row.
+// x: the stacked projection's rows (q channels, then k, then v: C = 2*G*dim + H*vdim columns from column 0 of `x`, rows
+// `ld` apart); taps [C, K] of x's type; history: float32 [K - 1, C] per slot at `hist` + slot * slot_stride.  Row t is
+// token (t - cu_new[b]) of sequence b = token_seq[t].  A value head's block also writes its head's decays and step size.
 template <typename T>
 __global__ void __launch_bounds__(DP_THREADS)
 delta_prepare_kernel(const T* __restrict__ x, int ld, const T* __restrict__ taps, int K, float* __restrict__ hist, long slot_stride,
@@ -40,56 +41,68 @@ delta_prepare_kernel(const T* __restrict__ x, int ld, const T* __restrict__ taps
                      const float* __restrict__ z, int z_stride, const float* __restrict__ dt_bias,
                      const float* __restrict__ a_log, float* __restrict__ qo, float* __restrict__ ko, float* __restrict__ vo,
                      float* __restrict__ go, float* __restrict__ bo, int H, int G, int dim, int vdim, float q_scale,
-                     float unit_eps, int update_history) {
-    extern __shared__ float dp_y[];                       // the token's q and k channels after convolution and silu
+                     float unit_eps, int update_history, int n_tokens, int per_block) {
+    extern __shared__ float dp_y[];                       // a query or key head's channels after convolution and silu
+    __shared__ float dp_r;
     dl_launch_dependents();
     dl_grid_dependency_wait();
-    const int t = blockIdx.x;
-    const int b = token_seq[t];
-    const int slot = slots[b];
-    if (slot < 0 || slot >= n_slots) return;
-    const int j = t - cu_new[b];                          // the token's place among its sequence's new tokens
+    const int part = blockIdx.y;
     const int qk = 2 * G * dim, C = qk + H * vdim;
-    float* hs = hist + (size_t)slot * slot_stride;
-    for (int c = threadIdx.x; c < C; c += DP_THREADS) {
-        float acc = 0.f;
-        for (int i = 0; i < K; ++i) {
-            const int lag = K - 1 - i;                    // tap i meets the input `lag` tokens back
-            float in;
-            if (lag <= j) in = dl_to_f32<T>(x[(size_t)(t - lag) * ld + c]);
-            else in = hs[(size_t)(K - 1 + j - lag) * C + c];      // before this step: the slot's history (zeros at the start)
-            acc = fmaf(dl_to_f32<T>(taps[(size_t)c * K + i]), in, acc);
+    const bool is_v = part >= 2 * G;
+    const int c0 = is_v ? qk + (part - 2 * G) * vdim : part * dim, width = is_v ? vdim : dim;
+    const int t_end = min(n_tokens, (blockIdx.x + 1) * per_block);
+    for (int t = blockIdx.x * per_block; t < t_end; ++t) {               // t, and all that hangs on it, is the block's
+        const int b = token_seq[t];
+        const int slot = slots[b];
+        if (slot < 0 || slot >= n_slots) continue;
+        const int j = t - cu_new[b];                      // the token's place among its sequence's new tokens
+        float* hs = hist + (size_t)slot * slot_stride;
+        for (int d = threadIdx.x; d < width; d += DP_THREADS) {
+            const int c = c0 + d;
+            float acc = 0.f;
+            for (int i = 0; i < K; ++i) {
+                const int lag = K - 1 - i;                // tap i meets the input `lag` tokens back
+                // new rows hold the last j inputs; older ones lie in the history, whose row K - 2 is the newest
+                const float in = lag <= j ? dl_to_f32<T>(x[(size_t)(t - lag) * ld + c])
+                                          : hs[(size_t)(K - 1 - (lag - j)) * C + c];
+                acc = fmaf(dl_to_f32<T>(taps[(size_t)c * K + i]), in, acc);
+            }
+            const float y = acc / (1.0f + expf(-acc));
+            if (is_v) vo[(size_t)t * H * vdim + (c - qk)] = y;
+            else dp_y[d] = y;
+            if (update_history) {
+                // a step of one token a sequence: this thread is the only reader of the channel's history and moves it on itself
+                for (int i = 0; i + 1 < K - 1; ++i) hs[(size_t)i * C + c] = hs[(size_t)(i + 1) * C + c];
+                if (K > 1) hs[(size_t)(K - 2) * C + c] = dl_to_f32<T>(x[(size_t)t * ld + c]);
+            }
         }
-        const float y = acc / (1.0f + expf(-acc));
-        if (c < qk) dp_y[c] = y;
-        else vo[(size_t)t * H * vdim + (c - qk)] = y;
-        if (update_history) {
-            // a step of one token a sequence: this block is the only reader of the slot's history and moves it on itself
-            for (int i = 0; i + 1 < K - 1; ++i) hs[(size_t)i * C + c] = hs[(size_t)(i + 1) * C + c];
-            if (K > 1) hs[(size_t)(K - 2) * C + c] = dl_to_f32<T>(x[(size_t)t * ld + c]);
+        if (is_v) {
+            const int h = part - 2 * G;
+            const float rate = expf(a_log[h]);
+            for (int d = threadIdx.x; d < dim; d += DP_THREADS) {
+                const int e = h * dim + d;
+                go[(size_t)t * H * dim + e] = expf(-rate * dr_softplus(z[(size_t)t * z_stride + e] + dt_bias[e]));
+            }
+            if (threadIdx.x == 0) bo[(size_t)t * H + h] = 1.0f / (1.0f + expf(-dl_to_f32<T>(b_logit[(size_t)t * b_stride + h])));
+            continue;
         }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float ss = 0.f;
+            for (int d = threadIdx.x; d < dim; d += 32) ss += dp_y[d] * dp_y[d];
+            ss = dl_warp_sum(ss);
+            if (threadIdx.x == 0) dp_r = (1.0f / sqrtf(ss + unit_eps)) * (part < G ? q_scale : 1.0f);
+        }
+        __syncthreads();
+        const float r = dp_r;
+        float* dst = part < G ? qo + (size_t)t * G * dim + (size_t)part * dim : ko + (size_t)t * G * dim + (size_t)(part - G) * dim;
+        for (int d = threadIdx.x; d < dim; d += DP_THREADS) dst[d] = dp_y[d] * r;
+        __syncthreads();                                  // the next token's channels take these places
     }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int head = warp; head < 2 * G; head += DP_THREADS / 32) {          // q heads, then k heads
-        const float* y = dp_y + (size_t)head * dim;
-        float ss = 0.f;
-        for (int d = lane; d < dim; d += 32) ss += y[d] * y[d];
-        ss = dl_warp_sum(ss);
-        const float r = (1.0f / sqrtf(ss + unit_eps)) * (head < G ? q_scale : 1.0f);
-        float* dst = head < G ? qo + (size_t)t * G * dim + (size_t)head * dim : ko + (size_t)t * G * dim + (size_t)(head - G) * dim;
-        for (int d = lane; d < dim; d += 32) dst[d] = y[d] * r;
-    }
-    for (int e = threadIdx.x; e < H * dim; e += DP_THREADS) {
-        const float rate = expf(a_log[e / dim]);
-        go[(size_t)t * H * dim + e] = expf(-rate * dr_softplus(z[(size_t)t * z_stride + e] + dt_bias[e]));
-    }
-    for (int h = threadIdx.x; h < H; h += DP_THREADS)
-        bo[(size_t)t * H + h] = 1.0f / (1.0f + expf(-dl_to_f32<T>(b_logit[(size_t)t * b_stride + h])));
 }
 
-// The history after a step of any shape: the last K - 1 inputs of each sequence, oldest first.  One block per sequence;
-// runs behind delta_prepare (which read the old history).
+// The history after a step of any shape: the last K - 1 inputs of each sequence, oldest first.  One thread per (sequence,
+// channel); runs behind delta_prepare (which read the old history).
 template <typename T>
 __global__ void __launch_bounds__(DP_THREADS)
 delta_history_kernel(const T* __restrict__ x, int ld, int K, float* __restrict__ hist, long slot_stride, int n_slots,
@@ -102,11 +115,12 @@ delta_history_kernel(const T* __restrict__ x, int ld, int K, float* __restrict__
     if (slot < 0 || slot >= n_slots || n <= 0) return;
     float* hs = hist + (size_t)slot * slot_stride;
     const int keep = K - 1;
-    for (int c = threadIdx.x; c < C; c += DP_THREADS)
-        for (int i = 0; i < keep; ++i) {                  // ascending: a place is read (at i + n) before it is written
-            const int src = i + n;                        // index in (old history ++ new inputs)
-            hs[(size_t)i * C + c] = src < keep ? hs[(size_t)src * C + c] : dl_to_f32<T>(x[(size_t)(t0 + src - keep) * ld + c]);
-        }
+    const int c = blockIdx.y * DP_THREADS + threadIdx.x;
+    if (c >= C) return;
+    for (int i = 0; i < keep; ++i) {                      // ascending: a place is read (at i + n) before it is written
+        const int src = i + n;                            // index in (old history ++ new inputs)
+        hs[(size_t)i * C + c] = src < keep ? hs[(size_t)src * C + c] : dl_to_f32<T>(x[(size_t)(t0 + src - keep) * ld + c]);
+    }
 }
 
 #define DR_SPLIT 8                                        // lanes that share a column
@@ -188,38 +202,56 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         if (tid < BATCH) sb[buf][tid] = rb;
         __syncthreads();                                  // the batch is staged (and every lane is done with the other buffer's batch before it is refilled)
         if (first + BATCH < t1) fetch(first + BATCH, min(BATCH, t1 - first - BATCH));
-        for (int i = 0; i < count; ++i) {
-            const float vt = sv[buf][i * DR_COLS + c_local];
-            const float bt = sb[buf][i];
+        // The operands of a token are read into registers while the token before it is walked.  Between two states lie only
+        // the dot product with g k, its shuffles, the step and one multiply-add: (g S)^T k = S^T (g k), and S' = g S + k u^T.
+        // The read-out o = S'^T q hangs on the new state but nothing hangs on it, so its sums and shuffles run beside the
+        // next token's chain.
+        float4 nq[ROWS / 4], nk[ROWS / 4], ng[ROWS / 4];
+        float nv, nb;
+        auto operands = [&](int i) {
             const float4* aq = reinterpret_cast<const float4*>(sq[buf] + i * ROW + r * RUN);
             const float4* ak = reinterpret_cast<const float4*>(sk[buf] + i * ROW + r * RUN);
             const float4* ag = reinterpret_cast<const float4*>(sg[buf] + i * ROW + r * RUN);
-            float pk[4] = {0.f, 0.f, 0.f, 0.f}, pq[4] = {0.f, 0.f, 0.f, 0.f}, qk[4] = {0.f, 0.f, 0.f, 0.f};
-            float kk[ROWS];
+#pragma unroll
+            for (int m = 0; m < ROWS / 4; ++m) nq[m] = aq[m], nk[m] = ak[m], ng[m] = ag[m];
+            nv = sv[buf][i * DR_COLS + c_local];
+            nb = sb[buf][i];
+        };
+        constexpr bool AHEAD = ROWS <= 16;                // wider runs leave no registers for a second set of operands
+        if (AHEAD) operands(0);
+        float* o_at = out + (size_t)first * H * vdim + h * vdim + col;
+#pragma unroll(AHEAD ? 2 : 1)
+        for (int i = 0; i < count; ++i, o_at += (size_t)H * vdim) {
+            if (!AHEAD) operands(i);
+            float kk[ROWS], gg[ROWS], qq[ROWS];
+            const float vt = nv, bt = nb;
 #pragma unroll
             for (int m = 0; m < ROWS / 4; ++m) {
-                const float4 g4 = ag[m], k4 = ak[m], q4 = aq[m];
-                s[4 * m] *= g4.x, s[4 * m + 1] *= g4.y, s[4 * m + 2] *= g4.z, s[4 * m + 3] *= g4.w;
+                const float4 g4 = ng[m], k4 = nk[m], q4 = nq[m];
                 kk[4 * m] = k4.x, kk[4 * m + 1] = k4.y, kk[4 * m + 2] = k4.z, kk[4 * m + 3] = k4.w;
-                pk[0] = fmaf(s[4 * m], k4.x, pk[0]), pk[1] = fmaf(s[4 * m + 1], k4.y, pk[1]);
-                pk[2] = fmaf(s[4 * m + 2], k4.z, pk[2]), pk[3] = fmaf(s[4 * m + 3], k4.w, pk[3]);
-                pq[0] = fmaf(s[4 * m], q4.x, pq[0]), pq[1] = fmaf(s[4 * m + 1], q4.y, pq[1]);
-                pq[2] = fmaf(s[4 * m + 2], q4.z, pq[2]), pq[3] = fmaf(s[4 * m + 3], q4.w, pq[3]);
-                qk[0] = fmaf(q4.x, k4.x, qk[0]), qk[1] = fmaf(q4.y, k4.y, qk[1]);
-                qk[2] = fmaf(q4.z, k4.z, qk[2]), qk[3] = fmaf(q4.w, k4.w, qk[3]);
+                gg[4 * m] = g4.x, gg[4 * m + 1] = g4.y, gg[4 * m + 2] = g4.z, gg[4 * m + 3] = g4.w;
+                qq[4 * m] = q4.x, qq[4 * m + 1] = q4.y, qq[4 * m + 2] = q4.z, qq[4 * m + 3] = q4.w;
             }
-            float sk_ = (pk[0] + pk[1]) + (pk[2] + pk[3]), sq_ = (pq[0] + pq[1]) + (pq[2] + pq[3]);
-            float qk_ = (qk[0] + qk[1]) + (qk[2] + qk[3]);
+            if (AHEAD) operands(min(i + 1, BATCH - 1));   // the next token's (the batch's last reads a staged place again)
+            float pk[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int o = DR_SPLIT / 2; o > 0; o >>= 1) {
-                sk_ += __shfl_xor_sync(0xffffffffu, sk_, o);
-                sq_ += __shfl_xor_sync(0xffffffffu, sq_, o);
-                qk_ += __shfl_xor_sync(0xffffffffu, qk_, o);
-            }
+            for (int m = 0; m < ROWS; ++m) pk[m & 3] = fmaf(s[m], gg[m] * kk[m], pk[m & 3]);
+            float sk_ = (pk[0] + pk[1]) + (pk[2] + pk[3]);
+#pragma unroll
+            for (int m = 0; m < ROWS; ++m) s[m] *= gg[m];
+#pragma unroll
+            for (int o = DR_SPLIT / 2; o > 0; o >>= 1) sk_ += __shfl_xor_sync(0xffffffffu, sk_, o);
             const float u = bt * (vt - sk_);
+            float pq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int m = 0; m < ROWS; ++m) s[m] = fmaf(kk[m], u, s[m]);
-            if (r == 0 && col_ok) out[(size_t)(first + i) * H * vdim + h * vdim + col] = fmaf(qk_, u, sq_);
+            for (int m = 0; m < ROWS; ++m) {
+                s[m] = fmaf(kk[m], u, s[m]);
+                pq[m & 3] = fmaf(s[m], qq[m], pq[m & 3]);
+            }
+            float sq_ = (pq[0] + pq[1]) + (pq[2] + pq[3]);
+#pragma unroll
+            for (int o = DR_SPLIT / 2; o > 0; o >>= 1) sq_ += __shfl_xor_sync(0xffffffffu, sq_, o);
+            if (r == 0 && col_ok) *o_at = sq_;
         }
         buf ^= 1;
     }
@@ -249,29 +281,31 @@ extern "C" int dl_delta_rule(const void* x, int ld, const void* taps, int K, int
     const int C = 2 * G * dim + H * vdim;
     DL_REQUIRE(ld >= C && z_stride >= H * dim && b_stride >= H, "delta_rule: rows overlap");
     DL_REQUIRE(dtype == DL_F32 || dtype == DL_BF16, "delta_rule: dtype %d", dtype);
-    const size_t smem = (size_t)2 * G * dim * sizeof(float);
-    DL_REQUIRE(smem <= 48 * 1024, "delta_rule: %d query and key channels are more than the kernel's shared memory takes", 2 * G * dim);
+    const size_t smem = (size_t)dim * sizeof(float);
     if (n_seqs == 0 || n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const bool single = n_tokens == n_seqs;               // every sequence brings exactly one token
+    // enough blocks for a few rounds over the machine; beyond that a block walks a run of tokens
+    const long rounds = (long)n_tokens * (2 * G + H) / 4096;
+    const int per_block = rounds < 1 ? 1 : rounds > 16 ? 16 : (int)rounds;
     cudaError_t e;
     if (dtype == DL_F32)
-        e = dl_launch_dependent(delta_prepare_kernel<float>, dim3(n_tokens), dim3(DP_THREADS), smem, s, (const float*)x, ld,
+        e = dl_launch_dependent(delta_prepare_kernel<float>, dim3((n_tokens + per_block - 1) / per_block, 2 * G + H), dim3(DP_THREADS), smem, s, (const float*)x, ld,
                                 (const float*)taps, K, hist, slot_stride, n_slots, token_seq, cu_new, slots, (const float*)b_logit,
                                 b_stride, z, z_stride, dt_bias, a_log, qo, ko, vo, go, bo, H, G, dim, vdim, q_scale, unit_eps,
-                                single ? 1 : 0);
+                                single ? 1 : 0, n_tokens, per_block);
     else
-        e = dl_launch_dependent(delta_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(DP_THREADS), smem, s,
+        e = dl_launch_dependent(delta_prepare_kernel<__nv_bfloat16>, dim3((n_tokens + per_block - 1) / per_block, 2 * G + H), dim3(DP_THREADS), smem, s,
                                 (const __nv_bfloat16*)x, ld, (const __nv_bfloat16*)taps, K, hist, slot_stride, n_slots, token_seq,
                                 cu_new, slots, (const __nv_bfloat16*)b_logit, b_stride, z, z_stride, dt_bias, a_log, qo, ko, vo,
-                                go, bo, H, G, dim, vdim, q_scale, unit_eps, single ? 1 : 0);
+                                go, bo, H, G, dim, vdim, q_scale, unit_eps, single ? 1 : 0, n_tokens, per_block);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "delta_prepare: %s", cudaGetErrorString(e));
     if (!single && K > 1) {
         if (dtype == DL_F32)
-            e = dl_launch_dependent(delta_history_kernel<float>, dim3(n_seqs), dim3(DP_THREADS), 0, s, (const float*)x, ld, K, hist,
+            e = dl_launch_dependent(delta_history_kernel<float>, dim3(n_seqs, (C + DP_THREADS - 1) / DP_THREADS), dim3(DP_THREADS), 0, s, (const float*)x, ld, K, hist,
                                     slot_stride, n_slots, cu_new, slots, C);
         else
-            e = dl_launch_dependent(delta_history_kernel<__nv_bfloat16>, dim3(n_seqs), dim3(DP_THREADS), 0, s,
+            e = dl_launch_dependent(delta_history_kernel<__nv_bfloat16>, dim3(n_seqs, (C + DP_THREADS - 1) / DP_THREADS), dim3(DP_THREADS), 0, s,
                                     (const __nv_bfloat16*)x, ld, K, hist, slot_stride, n_slots, cu_new, slots, C);
         if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "delta_history: %s", cudaGetErrorString(e));
     }
