@@ -39,11 +39,31 @@ int dl_fail(int status, const char* fmt, ...);
 // wrote and before it writes any global memory (an earlier kernel may still be reading it); what
 // it does before the wait may touch only memory that no kernel of the stream writes (weights).
 // dl_launch_dependents() is harmless in a kernel that nothing depends on.
+extern "C" int dl_sm_count();
 bool dl_dependent_launch_enabled();          // false when DOTLLM_DEPENDENT_LAUNCH=0 is set
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void dl_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// `early` false: the kernel starts only when its predecessor has ended, whatever that one announced.  For a grid of few,
+// long-running blocks: blocks that start early are placed wherever the predecessor's blocks leave room, several to a
+// multiprocessor, and stay there while other multiprocessors run empty.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dl_launch_dependent_if(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                                 cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = early && dl_dependent_launch_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t dl_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

@@ -25,6 +25,8 @@
 #include "common.cuh"
 
 #define DP_THREADS 128
+#define DP_RUN 16                                          // tokens a block walks in a row, at most
+#define DP_MAX_TAPS 16                                     // taps of the short convolution a thread keeps in registers
 
 __device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
@@ -33,7 +35,9 @@ __device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : lo
 // x: the stacked projection's rows (q channels, then k, then v: C = 2*G*dim + H*vdim columns from column 0 of `x`, rows
 // `ld` apart); taps [C, K] of x's type; history: float32 [K - 1, C] per slot at `hist` + slot * slot_stride.  Row t is
 // token (t - cu_new[b]) of sequence b = token_seq[t].  A value head's block also writes its head's decays and step size.
-template <typename T>
+// A thread keeps its channel's taps and last inputs in registers (KMAX >= K places, the current token's last, zeros in
+// front), moves them on by one place per token, and fills them anew where the run enters another sequence.
+template <typename T, int KMAX>
 __global__ void __launch_bounds__(DP_THREADS)
 delta_prepare_kernel(const T* __restrict__ x, int ld, const T* __restrict__ taps, int K, float* __restrict__ hist, long slot_stride,
                      int n_slots, const int32_t* __restrict__ token_seq, const int32_t* __restrict__ cu_new,
@@ -42,62 +46,102 @@ delta_prepare_kernel(const T* __restrict__ x, int ld, const T* __restrict__ taps
                      const float* __restrict__ a_log, float* __restrict__ qo, float* __restrict__ ko, float* __restrict__ vo,
                      float* __restrict__ go, float* __restrict__ bo, int H, int G, int dim, int vdim, float q_scale,
                      float unit_eps, int update_history, int n_tokens, int per_block) {
-    extern __shared__ float dp_y[];                       // a query or key head's channels after convolution and silu
-    __shared__ float dp_r;
+    extern __shared__ float dp_y[];                       // [per_block, dim]: a query or key head's channels after convolution and silu
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int part = blockIdx.y;
     const int qk = 2 * G * dim, C = qk + H * vdim;
     const bool is_v = part >= 2 * G;
     const int c0 = is_v ? qk + (part - 2 * G) * vdim : part * dim, width = is_v ? vdim : dim;
-    const int t_end = min(n_tokens, (blockIdx.x + 1) * per_block);
-    for (int t = blockIdx.x * per_block; t < t_end; ++t) {               // t, and all that hangs on it, is the block's
-        const int b = token_seq[t];
-        const int slot = slots[b];
-        if (slot < 0 || slot >= n_slots) continue;
-        const int j = t - cu_new[b];                      // the token's place among its sequence's new tokens
-        float* hs = hist + (size_t)slot * slot_stride;
-        for (int d = threadIdx.x; d < width; d += DP_THREADS) {
-            const int c = c0 + d;
-            float acc = 0.f;
-            for (int i = 0; i < K; ++i) {
-                const int lag = K - 1 - i;                // tap i meets the input `lag` tokens back
+    const int t_begin = blockIdx.x * per_block, t_end = min(n_tokens, t_begin + per_block);
+    __shared__ int dp_seq[DP_RUN], dp_slot[DP_RUN], dp_place[DP_RUN];   // per token of the run; a slot outside the memory reads -1
+    if (threadIdx.x < t_end - t_begin) {
+        const int b = token_seq[t_begin + threadIdx.x], slot = slots[b];
+        dp_seq[threadIdx.x] = b;
+        dp_slot[threadIdx.x] = slot >= 0 && slot < n_slots ? slot : -1;
+        dp_place[threadIdx.x] = t_begin + threadIdx.x - cu_new[b];
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < width; d += DP_THREADS) {
+        const int c = c0 + d;
+        float tap[KMAX], in[KMAX];
+#pragma unroll
+        for (int i = 0; i < KMAX; ++i) {                  // place KMAX - 1 - lag meets the input `lag` tokens back
+            const int lag = KMAX - 1 - i;
+            tap[i] = lag < K ? dl_to_f32<T>(taps[(size_t)c * K + (K - 1 - lag)]) : 0.f;
+            in[i] = 0.f;
+        }
+        int before = -1;
+        float ahead = dl_to_f32<T>(x[(size_t)t_begin * ld + c]);
+        for (int t = t_begin; t < t_end; ++t) {
+            const float now = ahead;                      // the next token's input is under way while this one is worked on
+            if (t + 1 < t_end) ahead = dl_to_f32<T>(x[(size_t)(t + 1) * ld + c]);
+            const int b = dp_seq[t - t_begin], slot = dp_slot[t - t_begin];
+            if (slot < 0) { before = -1; continue; }
+            const int j = dp_place[t - t_begin];          // the token's place among its sequence's new tokens
+            float* hs = hist + (size_t)slot * slot_stride;
+            if (b != before) {
                 // new rows hold the last j inputs; older ones lie in the history, whose row K - 2 is the newest
-                const float in = lag <= j ? dl_to_f32<T>(x[(size_t)(t - lag) * ld + c])
-                                          : hs[(size_t)(K - 1 - (lag - j)) * C + c];
-                acc = fmaf(dl_to_f32<T>(taps[(size_t)c * K + i]), in, acc);
+#pragma unroll
+                for (int lag = 1; lag < KMAX; ++lag)
+                    if (lag < K)
+                        in[KMAX - 1 - lag] = lag <= j ? dl_to_f32<T>(x[(size_t)(t - lag) * ld + c])
+                                                      : hs[(size_t)(K - 1 - (lag - j)) * C + c];
+                before = b;
             }
+            in[KMAX - 1] = now;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < KMAX; ++i) acc = fmaf(tap[i], in[i], acc);          // oldest first; a place in front of the taps adds 0 * 0
+#pragma unroll
+            for (int i = 0; i + 1 < KMAX; ++i) in[i] = in[i + 1];
             const float y = acc / (1.0f + expf(-acc));
             if (is_v) vo[(size_t)t * H * vdim + (c - qk)] = y;
-            else dp_y[d] = y;
+            else dp_y[(t - t_begin) * dim + d] = y;
             if (update_history) {
                 // a step of one token a sequence: this thread is the only reader of the channel's history and moves it on itself
                 for (int i = 0; i + 1 < K - 1; ++i) hs[(size_t)i * C + c] = hs[(size_t)(i + 1) * C + c];
-                if (K > 1) hs[(size_t)(K - 2) * C + c] = dl_to_f32<T>(x[(size_t)t * ld + c]);
+                if (K > 1) hs[(size_t)(K - 2) * C + c] = now;
             }
         }
-        if (is_v) {
-            const int h = part - 2 * G;
-            const float rate = expf(a_log[h]);
-            for (int d = threadIdx.x; d < dim; d += DP_THREADS) {
-                const int e = h * dim + d;
-                go[(size_t)t * H * dim + e] = expf(-rate * dr_softplus(z[(size_t)t * z_stride + e] + dt_bias[e]));
+    }
+    if (is_v) {
+        const int h = part - 2 * G;
+        const float rate = expf(a_log[h]);
+        const int items = (t_end - t_begin) * dim;         // (token, key channel) pairs, four loads of a thread under way
+        for (int first = threadIdx.x; first < items; first += 4 * DP_THREADS) {
+            float zs[4];
+            int at[4], ch[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = first + u * DP_THREADS;
+                at[u] = t_begin + idx / dim, ch[u] = h * dim + idx % dim;
+                zs[u] = idx < items ? z[(size_t)at[u] * z_stride + ch[u]] : 0.f;
             }
-            if (threadIdx.x == 0) bo[(size_t)t * H + h] = 1.0f / (1.0f + expf(-dl_to_f32<T>(b_logit[(size_t)t * b_stride + h])));
-            continue;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (first + u * DP_THREADS >= items) break;
+                if (dp_slot[at[u] - t_begin] < 0) continue;
+                go[(size_t)at[u] * H * dim + ch[u]] = expf(-rate * dr_softplus(zs[u] + dt_bias[ch[u]]));
+            }
         }
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            float ss = 0.f;
-            for (int d = threadIdx.x; d < dim; d += 32) ss += dp_y[d] * dp_y[d];
-            ss = dl_warp_sum(ss);
-            if (threadIdx.x == 0) dp_r = (1.0f / sqrtf(ss + unit_eps)) * (part < G ? q_scale : 1.0f);
+        for (int t = t_begin + threadIdx.x; t < t_end; t += DP_THREADS) {
+            if (dp_slot[t - t_begin] < 0) continue;
+            bo[(size_t)t * H + h] = 1.0f / (1.0f + expf(-dl_to_f32<T>(b_logit[(size_t)t * b_stride + h])));
         }
-        __syncthreads();
-        const float r = dp_r;
+        return;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    for (int t = t_begin + (threadIdx.x >> 5); t < t_end; t += DP_THREADS / 32) {  // a warp per token
+        if (dp_slot[t - t_begin] < 0) continue;
+        const float* y = dp_y + (t - t_begin) * dim;
+        float ss = 0.f;
+        for (int d = lane; d < dim; d += 32) ss += y[d] * y[d];
+        ss = dl_warp_sum(ss);
+        const float r = (1.0f / sqrtf(ss + unit_eps)) * (part < G ? q_scale : 1.0f);
         float* dst = part < G ? qo + (size_t)t * G * dim + (size_t)part * dim : ko + (size_t)t * G * dim + (size_t)(part - G) * dim;
-        for (int d = threadIdx.x; d < dim; d += DP_THREADS) dst[d] = dp_y[d] * r;
-        __syncthreads();                                  // the next token's channels take these places
+        for (int d = lane; d < dim; d += 32) dst[d] = y[d] * r;
     }
 }
 
@@ -277,28 +321,31 @@ extern "C" int dl_delta_rule(const void* x, int ld, const void* taps, int K, int
                              void* stream) {
     DL_REQUIRE(n_seqs >= 0 && n_tokens >= 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && n_slots > 0 && K >= 1, "delta_rule: bad sizes");
     DL_REQUIRE(H % G == 0, "delta_rule: %d heads are not a multiple of %d key heads", H, G);
+    DL_REQUIRE(K <= DP_MAX_TAPS, "delta_rule: a convolution of %d taps, the kernel takes up to %d", K, DP_MAX_TAPS);
     DL_REQUIRE(dim <= DR_MAX_DIM, "delta_rule: %d key channels per head, the kernel takes up to %d", dim, DR_MAX_DIM);
     const int C = 2 * G * dim + H * vdim;
     DL_REQUIRE(ld >= C && z_stride >= H * dim && b_stride >= H, "delta_rule: rows overlap");
     DL_REQUIRE(dtype == DL_F32 || dtype == DL_BF16, "delta_rule: dtype %d", dtype);
-    const size_t smem = (size_t)dim * sizeof(float);
     if (n_seqs == 0 || n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const bool single = n_tokens == n_seqs;               // every sequence brings exactly one token
     // enough blocks for a few rounds over the machine; beyond that a block walks a run of tokens
     const long rounds = (long)n_tokens * (2 * G + H) / 4096;
-    const int per_block = rounds < 1 ? 1 : rounds > 16 ? 16 : (int)rounds;
+    const int per_block = rounds < 1 ? 1 : rounds > DP_RUN ? DP_RUN : (int)rounds;
+    const size_t smem = (size_t)per_block * dim * sizeof(float);
     cudaError_t e;
-    if (dtype == DL_F32)
-        e = dl_launch_dependent(delta_prepare_kernel<float>, dim3((n_tokens + per_block - 1) / per_block, 2 * G + H), dim3(DP_THREADS), smem, s, (const float*)x, ld,
-                                (const float*)taps, K, hist, slot_stride, n_slots, token_seq, cu_new, slots, (const float*)b_logit,
-                                b_stride, z, z_stride, dt_bias, a_log, qo, ko, vo, go, bo, H, G, dim, vdim, q_scale, unit_eps,
-                                single ? 1 : 0, n_tokens, per_block);
-    else
-        e = dl_launch_dependent(delta_prepare_kernel<__nv_bfloat16>, dim3((n_tokens + per_block - 1) / per_block, 2 * G + H), dim3(DP_THREADS), smem, s,
-                                (const __nv_bfloat16*)x, ld, (const __nv_bfloat16*)taps, K, hist, slot_stride, n_slots, token_seq,
-                                cu_new, slots, (const __nv_bfloat16*)b_logit, b_stride, z, z_stride, dt_bias, a_log, qo, ko, vo,
-                                go, bo, H, G, dim, vdim, q_scale, unit_eps, single ? 1 : 0, n_tokens, per_block);
+    const dim3 pgrid((n_tokens + per_block - 1) / per_block, 2 * G + H);
+#define DP_LAUNCH(T, KMAX)                                                                                                    \
+    e = dl_launch_dependent(delta_prepare_kernel<T, KMAX>, pgrid, dim3(DP_THREADS), smem, s, (const T*)x, ld, (const T*)taps, \
+                            K, hist, slot_stride, n_slots, token_seq, cu_new, slots, (const T*)b_logit, b_stride, z,          \
+                            z_stride, dt_bias, a_log, qo, ko, vo, go, bo, H, G, dim, vdim, q_scale, unit_eps,                 \
+                            single ? 1 : 0, n_tokens, per_block)
+    if (dtype == DL_F32) {
+        if (K <= 4) { DP_LAUNCH(float, 4); } else if (K <= 8) { DP_LAUNCH(float, 8); } else { DP_LAUNCH(float, DP_MAX_TAPS); }
+    } else {
+        if (K <= 4) { DP_LAUNCH(__nv_bfloat16, 4); } else if (K <= 8) { DP_LAUNCH(__nv_bfloat16, 8); } else { DP_LAUNCH(__nv_bfloat16, DP_MAX_TAPS); }
+    }
+#undef DP_LAUNCH
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "delta_prepare: %s", cudaGetErrorString(e));
     if (!single && K > 1) {
         if (dtype == DL_F32)
@@ -311,13 +358,15 @@ extern "C" int dl_delta_rule(const void* x, int ld, const void* taps, int K, int
     }
     const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs), block(DR_THREADS);
     const int rows = (dim + DR_SPLIT - 1) / DR_SPLIT;
+    // few blocks that walk a long run of tokens want a multiprocessor each: they start when the kernels before have ended
+    const bool early = (long)grid.x * grid.y * grid.z > 2L * dl_sm_count();
 #define DR_LAUNCH(R)                                                                                                          \
     if (single)                                                                                                               \
-        e = dl_launch_dependent(delta_scan_kernel<R, true>, grid, block, 0, s, (const float*)qo, (const float*)ko,            \
+        e = dl_launch_dependent_if(early, delta_scan_kernel<R, true>, grid, block, 0, s, (const float*)qo, (const float*)ko,            \
                                 (const float*)vo, (const float*)go, (const float*)bo, cu_new, slots, state, slot_stride,      \
                                 n_slots, out, H, G, dim, vdim);                                                               \
     else                                                                                                                      \
-        e = dl_launch_dependent(delta_scan_kernel<R, false>, grid, block, 0, s, (const float*)qo, (const float*)ko,           \
+        e = dl_launch_dependent_if(early, delta_scan_kernel<R, false>, grid, block, 0, s, (const float*)qo, (const float*)ko,           \
                                 (const float*)vo, (const float*)go, (const float*)bo, cu_new, slots, state, slot_stride,      \
                                 n_slots, out, H, G, dim, vdim)
     if (rows <= 4) { DR_LAUNCH(4); }

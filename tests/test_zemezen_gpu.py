@@ -101,7 +101,7 @@ def run_cuts(model, tokens, cuts):
 # ------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,dim,vdim,K", [(4, 2, 24, 20, 3), (2, 2, 64, 64, 4), (3, 3, 10, 7, 1), (6, 2, 16, 24, 5), (2, 1, 128, 128, 4),
-                                           (1, 1, 200, 33, 2), (2, 1, 512, 16, 2), (8, 8, 8, 130, 4)])
+                                           (1, 1, 200, 33, 2), (2, 1, 512, 16, 2), (8, 8, 8, 130, 4), (2, 1, 16, 12, 7), (1, 1, 8, 8, 11)])
 def test_delta_rule_kernels_alone(H, G, dim, vdim, K, dtype):
     """Convolutions with their history, unit lengths, step sizes, decays and the recurrence: a step of three unequal
     prompts (one of a single token, one shorter than the taps), a step of portions of two, one and eight tokens, then
@@ -129,6 +129,34 @@ def test_delta_rule_kernels_alone(H, G, dim, vdim, K, dtype):
         close(got, want, dtype, 3e-5, 3e-5)                                   # float32 from the convolution on in either run
         close(got_mem, want_mem, dtype, 3e-5, 3e-5)
     assert torch.equal(got_mem.cpu()[[0, 3, 6]], memory[[0, 3, 6]]) and float(got_mem[2].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K", [4, 6])
+def test_delta_rule_long_steps_of_several_sequences(K, dtype):
+    """Steps long enough that a block of the convolution's kernel walks a run of tokens: sequences begin and end inside
+    runs, one is a single token between two long ones, one is shorter than the taps; then the same sequences go on."""
+    H, G, dim, vdim = 8, 4, 8, 16
+    C = 2 * G * dim + H * vdim
+    n_state = H * dim * vdim
+    taps = g64(C, K, seed=1, scale=0.5).to(dtype)
+    dt_bias, a_log = g64(H * dim, seed=2).float(), g64(H, seed=3, scale=0.5).float()
+    memory = torch.zeros(6, n_state + (K - 1) * C)
+    slots = torch.tensor([4, 1, 5, 2], dtype=torch.int32)
+    want_mem, got_mem = memory.clone(), memory.clone().to(DEV)
+    dev = lambda t: t.to(DEV)
+    for round_, news in enumerate(([301, 1, 212, 2], [3, 170, 1, 401], [1, 1, 1, 1])):
+        T = sum(news)
+        x = g64(T, C + H, seed=30 + round_).to(dtype)
+        z = g64(T, H * dim, seed=40 + round_).float()
+        seq = torch.tensor([i for i, n in enumerate(news) for _ in range(n)], dtype=torch.int32)
+        cu = torch.tensor([0] + list(np.cumsum(news)), dtype=torch.int32)
+        want = kernel_refs.delta_rule(x, taps, x[:, C:], z, dt_bias, a_log, seq, cu, slots, want_mem, H, G, dim, vdim, dim ** -0.5, 1e-6)
+        gx = dev(x)
+        got = ops.delta_rule(gx, dev(taps), gx[:, C:], dev(z), dev(dt_bias), dev(a_log), dev(seq), dev(cu), dev(slots), got_mem,
+                             H, G, dim, vdim, dim ** -0.5, 1e-6)
+        close(got, want, dtype, 1e-4, 1e-4)
+        close(got_mem, want_mem, dtype, 1e-4, 1e-4)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
