@@ -81,7 +81,7 @@ CONFIGS = {
     # key/value head, a window longer than a page, more kept tokens than a page holds
     "B": config(128, 333, 1e-5,
                 [attention(8, 2, 64, 0.11, 70, 5, 64, mlp=dense(160)),
-                 delta(2, 2, 64, 64, 4, mlp=moe(8, 4, 64, groups=(4, 3))),
+                 delta(2, 2, 64, 64, 4, mlp=moe(10, 4, 64, groups=(5, 3))),
                  latent(4, 32, 48, 64, 0.17, mlp=dense(96)),
                  attention(4, 1, 128, 0.09, 130, 70, 64, 1000000.0, mlp=moe(4, 1, 32, groups=(4, 4)))]),
     # multiples of nothing: a width that is no multiple of 8, odd key and value widths, one tap, a window of one token,
