@@ -92,7 +92,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                             int n_pages, const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_row0,
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_new,
                             const int32_t* __restrict__ cu_new, const int32_t* __restrict__ block_table, int bt_stride,
-                            int nkv, int group, float scale, int window, int* __restrict__ status) {
+                            int nkv, int group, float scale, int window, int keep_first, const float* __restrict__ sinks,
+                            int* __restrict__ status) {
     constexpr int ATOMS = HD / 64;                           // 64-dim (128-byte) slices of a head
     constexpr int STAGES = PT_STAGES(HD);
     constexpr uint32_t Q_BYTES = PT_ROWS * HD * 2;
@@ -129,16 +130,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     }
     // The block walks the pages from the first one tile 0 sees to the last one its last live tile sees;
     // a tile joins at its own first page and leaves after its own last (the ranges overlap or touch).
+    // Kept first tokens: the pages that hold them and lie in front of the window's first page lead the walk (`extra`
+    // of them), so the walk starts at the sequence's first page, and every tile takes part from the walk's start; a
+    // page between a tile's kept pages and its own window is masked whole for it and adds zeros.
     const int page_lo = tiles[0].first_key / DL_PAGE;
+    const int extra = min((keep_first + DL_PAGE - 1) / DL_PAGE, page_lo);
     int page_hi = tiles[0].pos_last / DL_PAGE;
 #pragma unroll
     for (int t = 0; t < PT_TILES; ++t) {
         PtTile& T = tiles[t];
-        T.j_lo = T.first_key / DL_PAGE - page_lo;
-        T.j_hi = T.rows > 0 ? T.pos_last / DL_PAGE - page_lo : T.j_lo - 1;
+        T.j_lo = keep_first > 0 ? 0 : T.first_key / DL_PAGE - page_lo;   // with kept tokens the walk starts at page 0
+        T.j_hi = T.rows > 0 ? extra + T.pos_last / DL_PAGE - page_lo : T.j_lo - 1;
         if (T.rows > 0) page_hi = max(page_hi, T.pos_last / DL_PAGE);
     }
-    const int n_kv = page_hi - page_lo + 1;                  // pages this block walks
+    const int n_kv = extra + page_hi - page_lo + 1;          // pages this block walks
+    auto page_of = [&](int j) { return j < extra ? j : page_lo + (j - extra); };   // the walk's page j in the sequence
 
     if (threadIdx.x == 0) {
         gave_up = 0;
@@ -180,9 +186,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                                    cu_new[b] + row0 + t * PT_ROWS, &q_full[t]);
             }
         }
-        const int32_t* pages = block_table + (size_t)b * bt_stride + page_lo;
+        const int32_t* pages = block_table + (size_t)b * bt_stride;
         for (int j0 = 0; j0 < n_kv && !stop; j0 += 32) {
-            const int mine = (j0 + lane < n_kv) ? pages[j0 + lane] : 0;
+            const int mine = (j0 + lane < n_kv) ? pages[page_of(j0 + lane)] : 0;
             const int count = min(32, n_kv - j0);
             for (int jj = 0; jj < count; ++jj) {
                 const int page = __shfl_sync(0xffffffffu, mine, jj);
@@ -328,7 +334,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             if (lane == 0) tc_mbar_arrive(&s_empty[t][sb]);     // the score buffer may take the tile's page after next
             if (stamps) PT_STAMP(7, j);                         // scores read into registers
 
-            const int key0 = (page_lo + j) * DL_PAGE;
+            const int key0 = page_of(j) * DL_PAGE;
             // pages wholly visible to every row of the tile need no mask
             const bool ragged = T.rows < PT_ROWS || key0 + DL_PAGE - 1 > T.pos0 || key0 < T.first_key ||
                                 (window > 0 && key0 <= T.pos_last - window);
@@ -336,7 +342,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int key = key0 + i;
-                    const bool seen = live && key <= pos && (window == 0 || key > pos - window);
+                    const bool seen = live && key <= pos && (window == 0 || key > pos - window || key < keep_first);
                     if (!seen) sc[i] = -INFINITY;
                 }
             }
@@ -419,6 +425,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         if (!ok) gave_up = 1;
         if (ok && n_mine > 0) {
             tc_fence_after();
+            // the sink: one more term in the sum of weights, with no value; m_ref is in units of log2
+            if (sinks != nullptr && m_ref > -INFINITY) l += pt_ex2(fmaf(sinks[head], 1.4426950408889634f, -m_ref));
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* dst = out + (size_t)(cu_new[b] + row0 + t * PT_ROWS + r) * out_stride + (size_t)head * HD;
 #pragma unroll 1
@@ -481,7 +489,7 @@ template <int HD>
 static int pt_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, int n_tokens, void* out, int out_stride,
                      const void* k_pool, const void* v_pool, int n_pages, const int32_t* tile_seq, const int32_t* tile_row0,
                      const int32_t* seq_start, const int32_t* seq_new, const int32_t* cu_new, const int32_t* block_table,
-                     int bt_stride, int nh, int nkv, float scale, int window, int* status) {
+                     int bt_stride, int nh, int nkv, float scale, int window, int keep_first, const float* sinks, int* status) {
     const size_t smem = (size_t)PT_TILES * PT_ROWS * HD * 2 + (size_t)PT_STAGES(HD) * 2 * DL_PAGE * HD * 2 +
                         (size_t)PT_TILES * 2 * PT_ROWS * DL_PAGE * 2 + 1024;
     static bool configured = false;
@@ -499,7 +507,7 @@ static int pt_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, int
     if (rc != DL_OK) return rc;
     attention_prefill_tc_kernel<HD><<<grid, PT_THREADS, smem, s>>>(tmap_q, tmap_k, tmap_v, (__nv_bfloat16*)out, out_stride, n_pages,
                                                                   tile_seq, tile_row0, seq_start, seq_new, cu_new, block_table,
-                                                                  bt_stride, nkv, nh / nkv, scale, window, status);
+                                                                  bt_stride, nkv, nh / nkv, scale, window, keep_first, sinks, status);
     DL_CHECK_LAUNCH("attention_prefill_tc");
     return DL_OK;
 }
@@ -513,10 +521,11 @@ extern "C" int dl_attention_prefill_tc_bf16(const void* q, int q_stride, int n_t
                                             const void* k_pool, const void* v_pool, int n_pages, const int32_t* tile_seq,
                                             const int32_t* tile_row0, int n_tiles, const int32_t* seq_start,
                                             const int32_t* seq_new, const int32_t* cu_new, const int32_t* block_table,
-                                            int bt_stride, int nh, int nkv, int hd, float scale, int window, int* status,
-                                            void* stream) {
+                                            int bt_stride, int nh, int nkv, int hd, float scale, int window, int keep_first,
+                                            const float* sinks, int* status, void* stream) {
     DL_REQUIRE(n_tiles >= 0 && n_tokens >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill_tc: bad sizes");
     DL_REQUIRE(scale > 0.f && window >= 0, "attention_prefill_tc: the score scale must be positive, the window not negative");
+    DL_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention_prefill_tc: kept first tokens go with a window");
     DL_REQUIRE(status != nullptr, "attention_prefill_tc: needs a status word");
     DL_REQUIRE(q_stride % 8 == 0 && out_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
                    ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0,
@@ -530,9 +539,9 @@ extern "C" int dl_attention_prefill_tc_bf16(const void* q, int q_stride, int n_t
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64)
         return pt_launch<64>(grid, s, q, q_stride, n_tokens, out, out_stride, k_pool, v_pool, n_pages, tile_seq, tile_row0,
-                             seq_start, seq_new, cu_new, block_table, bt_stride, nh, nkv, scale, window, status);
+                             seq_start, seq_new, cu_new, block_table, bt_stride, nh, nkv, scale, window, keep_first, sinks, status);
     if (hd == 128)
         return pt_launch<128>(grid, s, q, q_stride, n_tokens, out, out_stride, k_pool, v_pool, n_pages, tile_seq, tile_row0,
-                              seq_start, seq_new, cu_new, block_table, bt_stride, nh, nkv, scale, window, status);
+                              seq_start, seq_new, cu_new, block_table, bt_stride, nh, nkv, scale, window, keep_first, sinks, status);
     return dl_fail(DL_ERR_UNSUPPORTED, "attention_prefill_tc: head_dim %d (takes 64 and 128)", hd);
 }

@@ -22,13 +22,14 @@ _library.register_signatures({
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                   _F, _I, _I, _P, _P, _P],
     "dl_attention_prefill_tc_bf16": [_P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                     _F, _I, _P, _P],
+                                     _F, _I, _I, _P, _P, _P],
 })
 
 PREFILL_ROWS = 128       # query rows per block of the mma.sync prefill kernel (AP_ROWS)
 PREFILL_TC_ROWS = 256    # ... and of the tcgen05 one (PT_TILES * PT_ROWS)
 PREFILL_TC_HEAD_DIMS = (64, 128)     # head sizes of the tcgen05 prefill kernel; others take the mma.sync one
 PREFILL_TC = True        # False: always the mma.sync kernel (tests compare the two)
+PREFILL_TC_SPECIAL = True    # False: prompts with kept first tokens or sinks take the mma.sync kernel at every head size
 
 DECODE_HEAD_DIMS = (32, 64, 96, 128)
 DECODE_SPECIAL = True    # False: decode steps with kept first tokens or sinks take the packed prefill kernel (tests compare the two)
@@ -138,9 +139,8 @@ def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_h
 
 def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads, head_dim,
              scale, window, plan, keep_first=0, sinks=None):
-    # kept first tokens and sinks are the mma.sync kernel's, at every head size
     tc = PREFILL_TC and head_dim in PREFILL_TC_HEAD_DIMS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 \
-        and not keep_first and sinks is None
+        and (PREFILL_TC_SPECIAL or (not keep_first and sinks is None))
     rows = PREFILL_TC_ROWS if tc else PREFILL_ROWS
     if ("prefill_tiles", rows) not in plan.scratch:
         # tiles that see the most keys first: the kernels start blocks in this order, and the short
@@ -158,6 +158,7 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
                       k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
                       n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),
                       block_table.data_ptr(), block_table.shape[1], n_heads, n_kv_heads, head_dim, scale, window,
+                      int(keep_first), None if sinks is None else sinks.data_ptr(),
                       _library.status_word(q.device).data_ptr(), _library.current_stream())
         return True
     _library.call("dl_attention_prefill_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
@@ -173,7 +174,8 @@ def run(q, q_stride, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_t
         n_heads, n_kv_heads, head_dim, scale, window, plan, keep_first=0, sinks=None):
     """Run a tensor-core kernel into ``out`` and return True, or return False to let the
     generic kernel take the call.  Kept first tokens and sinks are taken by the decode kernel (the kept pages join the
-    step's list of pages; the sink's term enters where a head is normalised) and by the packed mma.sync prefill kernel."""
+    step's list of pages; the sink's term enters where a head is normalised) and by both prefill kernels (the tcgen05 one
+    walks the kept pages ahead of the window's, the mma.sync one lists them per tile)."""
     if q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16 or head_dim not in DECODE_HEAD_DIMS:
         return False
     special = bool(keep_first) or sinks is not None

@@ -282,6 +282,55 @@ def test_windowed_attention_with_kept_tokens_and_sinks_alone(nh, nkv, hd, window
             assert float((no_sink.cpu() - want).abs().max()) > 1e-3
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,keep", [(4, 2, 64, 200, 4), (4, 1, 128, 130, 70), (2, 2, 128, 64, 64), (4, 4, 64, 300, 129),
+                                                  (2, 1, 128, 1, 1), (2, 2, 64, 1000, 200)])
+def test_long_prompts_with_kept_tokens_and_sinks_on_both_prompt_kernels(nh, nkv, hd, window, keep, monkeypatch):
+    """Prompts and portions of several hundred tokens in bfloat16, so that the window's first page lies well behind the kept
+    pages and the two tiles of a block start on different pages: the tcgen05 kernel and the mma.sync kernel against the plain
+    attention and against each other.  Pages between the kept ones and the step's first window are NaN."""
+    from dotllm_b200.engine.step import AttentionPlan
+    from dotllm_b200.kernels import attention_fast
+    dtype = torch.bfloat16
+    lens = [900, 333, 64, 700]
+    k_pool, v_pool, table = paged(lens, nkv, hd, dtype, 11)
+    gen = torch.Generator().manual_seed(3)
+    for b, n in enumerate(lens):
+        for p in range((n + 63) // 64):
+            page = int(table[b, p])
+            k_pool[page] = torch.randn(nkv, 64, hd, generator=gen).to(dtype)
+            v_pool[page] = torch.randn(nkv, hd, 64, generator=gen).to(dtype)
+    sinks = g64(nh, seed=9, scale=2.0).float()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    for starts, news in (([0, 0, 0, 0], [900, 333, 64, 700]), ([500, 300, 63, 1], [400, 33, 1, 699]), ([640, 0, 0, 448], [257, 2, 1, 129])):
+        T = sum(news)
+        seq = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32)
+        pos = torch.tensor([s + i for s, n in zip(starts, news) for i in range(n)], dtype=torch.int32)
+        q = (torch.randn(T, nh * hd, generator=gen) * 0.5).to(dtype)
+        want = kernel_refs.attention(q, k_pool, v_pool, seq, pos, table, nh, nkv, hd, 0.2, window, keep_first=keep, sinks=sinks)
+        totals = [s + n for s, n in zip(starts, news)]
+        hidden_k, hidden_v = k_pool.clone().to(DEV), v_pool.clone().to(DEV)
+        for b in range(len(lens)):
+            for p in range((keep + 63) // 64, max(0, (starts[b] - window + 1)) // 64):
+                hidden_k[int(table[b, p])] = float("nan")
+                hidden_v[int(table[b, p])] = float("nan")
+        outs = []
+        for special in (True, False):
+            monkeypatch.setattr(attention_fast, "PREFILL_TC_SPECIAL", special)
+            plan = AttentionPlan(len(lens), max(news), max(totals), False, i32(starts), i32(news),
+                                 i32([0] + list(np.cumsum(news))), i32(totals), list(starts), list(news))
+            got = ops.attention(q.to(DEV), hidden_k, hidden_v, seq.to(DEV), pos.to(DEV), table.to(DEV), nh, nkv, hd, 0.2, window,
+                                plan=plan, keep_first=keep, sinks=sinks.to(DEV))
+            assert torch.isfinite(got.float()).all()
+            close(got, want, dtype, 2e-5, 2e-2)
+            outs.append(got.float().cpu())
+        assert float((outs[0] - outs[1]).abs().max()) <= 2e-2
+        no_sink = ops.attention(q.to(DEV), hidden_k, hidden_v, seq.to(DEV), pos.to(DEV), table.to(DEV), nh, nkv, hd, 0.2, window,
+                                plan=AttentionPlan(len(lens), max(news), max(totals), False, i32(starts), i32(news),
+                                                   i32([0] + list(np.cumsum(news))), i32(totals), list(starts), list(news)),
+                                keep_first=keep)
+        assert float((no_sink.float().cpu() - want).abs().max()) > 1e-3
+
+
 @pytest.mark.parametrize("blocks", [0, 1, 3, 7])
 @pytest.mark.parametrize("nh,nkv,hd,window,keep", [(8, 2, 64, 100, 3), (4, 4, 128, 64, 64), (12, 1, 32, 70, 130), (6, 2, 96, 129, 65),
                                                   (4, 2, 64, 1, 1), (2, 1, 64, 640, 200)])
