@@ -1,5 +1,6 @@
 // Prefill attention on the fifth-generation tensor cores: packed new tokens of several sequences
-// over their paged bfloat16 cache, causal, optional sliding window.
+// over their paged bfloat16 cache, causal, optional sliding window, optionally with a sequence's first
+// tokens kept visible in front of the window and a learned number per head (a sink) in the softmax's sum.
 //
 // Role of the reference's attention_f16 with seq_q > 1 (native/kernels/attention.cu:19-197): scores
 // scaled by 1/sqrt(hd), softmax with the running maximum subtracted, weighted sum of values, query
@@ -516,7 +517,8 @@ static int pt_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, int
 // 256-row tile its sequence and its first row among that sequence's new tokens, best with the tiles
 // that see the most keys first.  seq_start,
 // seq_new: cached length before the step and new tokens, per sequence; cu_new: packed offsets.
-// head_dim 64 or 128.  status: int32, set non-zero if a wait expired.
+// head_dim 64 or 128.  keep_first: with a window, that many first tokens of a sequence stay visible; sinks: float32 [nh]
+// or null, exp(sinks[h]) joins head h's sum of weights.  status: int32, set non-zero if a wait expired.
 extern "C" int dl_attention_prefill_tc_bf16(const void* q, int q_stride, int n_tokens, void* out, int out_stride,
                                             const void* k_pool, const void* v_pool, int n_pages, const int32_t* tile_seq,
                                             const int32_t* tile_row0, int n_tiles, const int32_t* seq_start,

@@ -26,7 +26,7 @@
 
 #define DP_THREADS 128
 #define DP_RUN 16                                          // tokens a block walks in a row, at most
-#define DP_MAX_TAPS 16                                     // taps of the short convolution a thread keeps in registers
+#define DP_MAX_TAPS 64                                     // taps of the short convolution a thread keeps in registers
 
 __device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
@@ -341,9 +341,10 @@ extern "C" int dl_delta_rule(const void* x, int ld, const void* taps, int K, int
                             z_stride, dt_bias, a_log, qo, ko, vo, go, bo, H, G, dim, vdim, q_scale, unit_eps,                 \
                             single ? 1 : 0, n_tokens, per_block)
     if (dtype == DL_F32) {
-        if (K <= 4) { DP_LAUNCH(float, 4); } else if (K <= 8) { DP_LAUNCH(float, 8); } else { DP_LAUNCH(float, DP_MAX_TAPS); }
+        if (K <= 4) { DP_LAUNCH(float, 4); } else if (K <= 8) { DP_LAUNCH(float, 8); } else if (K <= 16) { DP_LAUNCH(float, 16); } else { DP_LAUNCH(float, DP_MAX_TAPS); }
     } else {
-        if (K <= 4) { DP_LAUNCH(__nv_bfloat16, 4); } else if (K <= 8) { DP_LAUNCH(__nv_bfloat16, 8); } else { DP_LAUNCH(__nv_bfloat16, DP_MAX_TAPS); }
+        if (K <= 4) { DP_LAUNCH(__nv_bfloat16, 4); } else if (K <= 8) { DP_LAUNCH(__nv_bfloat16, 8); } else if (K <= 16) { DP_LAUNCH(__nv_bfloat16, 16); }
+        else { DP_LAUNCH(__nv_bfloat16, DP_MAX_TAPS); }
     }
 #undef DP_LAUNCH
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "delta_prepare: %s", cudaGetErrorString(e));

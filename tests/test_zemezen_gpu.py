@@ -101,7 +101,7 @@ def run_cuts(model, tokens, cuts):
 # ------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,dim,vdim,K", [(4, 2, 24, 20, 3), (2, 2, 64, 64, 4), (3, 3, 10, 7, 1), (6, 2, 16, 24, 5), (2, 1, 128, 128, 4),
-                                           (1, 1, 200, 33, 2), (2, 1, 512, 16, 2), (8, 8, 8, 130, 4), (2, 1, 16, 12, 7), (1, 1, 8, 8, 11)])
+                                           (1, 1, 200, 33, 2), (2, 1, 512, 16, 2), (8, 8, 8, 130, 4), (2, 1, 16, 12, 7), (1, 1, 8, 8, 11), (2, 2, 8, 4, 20)])
 def test_delta_rule_kernels_alone(H, G, dim, vdim, K, dtype):
     """Convolutions with their history, unit lengths, step sizes, decays and the recurrence: a step of three unequal
     prompts (one of a single token, one shorter than the taps), a step of portions of two, one and eight tokens, then
