@@ -35,6 +35,7 @@ class ChannelDeltaMixer(Mixer):
              "rate": "A_log", "norm": "norm", "decay_in": "a1", "decay_out": "a2", "decay_bias": "dt_bias",
              "gate_in": "g1", "gate_out": "g2", "out": "o"}
     ROW_STEP = 16                # the stacked matrix's rows are a multiple of this: its product's rows stay 16-byte aligned
+    MAX_KEY_DIM, MAX_TAPS = 512, 64      # what the scan keeps in a lane's registers, and the convolution in a thread's
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
@@ -49,6 +50,9 @@ class ChannelDeltaMixer(Mixer):
         self.gate_rank = int(params.get("gate_rank", 16))
         if min(self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim, self.taps, self.decay_rank, self.gate_rank) <= 0:
             raise ConfigError("channel delta: heads, sizes and taps must be positive")
+        if self.key_dim > self.MAX_KEY_DIM or self.taps > self.MAX_TAPS:
+            raise ConfigError(f"channel delta: the kernels take up to {self.MAX_KEY_DIM} key channels a head and convolutions of up "
+                              f"to {self.MAX_TAPS} taps, not {self.key_dim} and {self.taps}")
         if self.n_heads % self.n_kv_heads:
             raise ConfigError(f"channel delta: {self.n_heads} heads are not a multiple of {self.n_kv_heads} query/key heads")
         self.names = dict(self.NAMES, **(params.get("tensors") or {}))

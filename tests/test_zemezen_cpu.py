@@ -42,6 +42,14 @@ def test_configuration_reads_every_key_and_writes_it_back():
             config_from_dict(bad)
 
 
+def test_sizes_beyond_the_delta_rules_kernels_are_refused_when_the_model_is_made():
+    for layer in (tz.delta(2, 2, 16, 8, 65), tz.delta(1, 1, 520, 8, 2)):
+        spec = build_spec(config_from_dict(tz.config(64, 100, 1e-5, [layer])))
+        with pytest.raises(ConfigError, match="channel delta"):
+            DecoderModel(spec, CPU)
+    DecoderModel(build_spec(config_from_dict(tz.config(64, 100, 1e-5, [tz.delta(1, 1, 512, 8, 64)]))), CPU)
+
+
 def test_description_schedule_tensor_names_and_cache_needs():
     spec = build_spec(config_from_dict(copy.deepcopy(tz.CONFIGS["A"])))
     assert [e.layer for e in spec.schedule] == [0, 1, 2, 3, 0, 2] and len(spec.layers) == 4
