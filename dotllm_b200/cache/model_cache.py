@@ -13,6 +13,8 @@ Here one object serves a batch:
   back once every token in them is older than the window (pages that hold a sequence's kept first tokens stay).  A "state" group holds a fixed-size
   tensor per slot, zeroed when a sequence opens;
 * an execution that reads another execution's cache gets a view of that storage and never writes;
+* an execution whose mixer is made of several that each keep something (attention beside a recurrence) names a tuple
+  of needs; each lives in the group of its kind, and the execution's view is a tuple of views in the same order;
 * one slot and one page per group beyond those the pools hand out (``idle_slot``, ``idle_page``): a
   step whose launch shapes are wider than its batch (a captured decode step that serves several
   batch sizes) points its idle rows there, as sequences of one token whose results nobody reads.
@@ -95,8 +97,8 @@ class CacheGroup:
 
 
 class ModelCache:
-    """``needs[e]`` is the CacheNeed of schedule entry e (None: keeps nothing); ``cache_of[e]`` is
-    None or the earlier entry whose storage entry e reads."""
+    """``needs[e]`` is the CacheNeed of schedule entry e (None: keeps nothing; a tuple: one per mixer of a mixer made of
+    several, kept under the keys (e, 0), (e, 1), ...); ``cache_of[e]`` is None or the earlier entry whose storage entry e reads."""
 
     def __init__(self, needs, cache_of, runtime, max_tokens, max_sequences=None):
         if max_tokens <= 0:
@@ -109,15 +111,20 @@ class ModelCache:
         self.slots = IdPool(self.n_slots, "slot")
         self.idle_slot, self.idle_page = self.n_slots, self.n_pages      # never handed out
         self.groups = []
-        self.entry_group = {}                       # schedule entry -> (group index, owner entry)
+        self.entry_group = {}                       # storage key -> (group index, owner key); a key is e, or (e, i) of a tuple
+        self.parts_of = {}                          # schedule entry whose need is a tuple -> how many
         by_key = {}
         for e, need in enumerate(needs):
             owner = cache_of[e] if cache_of[e] is not None else e
+            if isinstance(need, (tuple, list)):
+                self.parts_of[e] = len(need)
             if owner != e:
                 continue
             if need is None:
                 continue
-            by_key.setdefault(need.group_key(runtime.dtype), (need, []))[1].append(e)
+            for key, one in ([((e, i), n) for i, n in enumerate(need)] if e in self.parts_of else [(e, need)]):
+                if one is not None:
+                    by_key.setdefault(one.group_key(runtime.dtype), (one, []))[1].append(key)
         for key, (need, entries) in by_key.items():
             self.groups.append(CacheGroup(len(self.groups), need, entries, runtime, self.n_pages, self.n_slots))
         for g in self.groups:
@@ -126,9 +133,13 @@ class ModelCache:
         for e, need in enumerate(needs):
             owner = cache_of[e]
             if owner is not None:
-                if owner not in self.entry_group:
-                    raise CacheError(f"schedule entry {e} reads the cache of entry {owner}, which keeps none")
-                self.entry_group[e] = (self.entry_group[owner][0], owner)
+                if self.parts_of.get(owner) != self.parts_of.get(e):
+                    raise CacheError(f"schedule entry {e} reads the cache of entry {owner}, which keeps something else")
+                pairs = [((e, i), (owner, i)) for i in range(self.parts_of[e])] if e in self.parts_of else [(e, owner)]
+                for key, owner_key in pairs:
+                    if owner_key not in self.entry_group:
+                        raise CacheError(f"schedule entry {e} reads the cache of entry {owner}, which keeps none")
+                    self.entry_group[key] = (self.entry_group[owner_key][0], owner_key)
         self.kv_groups = [g for g in self.groups if g.kind == "kv"]
         self.live = {}                              # slot -> Sequence
 
@@ -221,6 +232,8 @@ class ModelCache:
     def view(self, entry, block_tables, slots):
         """The storage of schedule entry ``entry`` for this step.  ``block_tables[g]`` is the
         step's device block table of kv group g; ``slots`` the device slot ids of its sequences."""
+        if entry in self.parts_of:
+            return tuple(self.view((entry, i), block_tables, slots) for i in range(self.parts_of[entry]))
         if entry not in self.entry_group:
             return None
         gi, owner = self.entry_group[entry]

@@ -43,7 +43,7 @@ def registered_architectures():
 
 def _ensure_builtin():
     # Built-in architectures register themselves on import.
-    from ..models import komulorn, kubedra, llama, zemezen  # noqa: F401
+    from ..models import komulorn, kubedra, llama, sopalorn, zemezen  # noqa: F401
 
 
 def resolve_architecture(config_dict) -> Architecture:

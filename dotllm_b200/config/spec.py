@@ -28,7 +28,7 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerPart:
     """One part of a layer: the name its arrangement knows it by, its family ("mixer",
-    "feed_forward" or "norm") and its description."""
+    "feed_forward", "norm" or "connection") and its description."""
     name: str
     family: str
     spec: PartSpec
@@ -101,7 +101,7 @@ class ModelSpec:
             if len(set(names)) != len(names):
                 raise ConfigError(f"a layer names a part twice: {names}")
             for p in layer.parts:
-                if p.family not in ("mixer", "feed_forward", "norm"):
+                if p.family not in ("mixer", "feed_forward", "norm", "connection"):
                     raise ConfigError(f"layer part {p.name!r} has unknown family {p.family!r}")
         for n, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):

@@ -45,7 +45,7 @@ delta_prepare_kernel(const T* __restrict__ x, int ld, const T* __restrict__ taps
                      const float* __restrict__ z, int z_stride, const float* __restrict__ dt_bias,
                      const float* __restrict__ a_log, float* __restrict__ qo, float* __restrict__ ko, float* __restrict__ vo,
                      float* __restrict__ go, float* __restrict__ bo, int H, int G, int dim, int vdim, float q_scale,
-                     float unit_eps, int update_history, int n_tokens, int per_block) {
+                     float unit_eps, int update_history, int n_tokens, int per_block, int head_decay) {
     extern __shared__ float dp_y[];                       // [per_block, dim]: a query or key head's channels after convolution and silu
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -116,13 +116,13 @@ delta_prepare_kernel(const T* __restrict__ x, int ld, const T* __restrict__ taps
             for (int u = 0; u < 4; ++u) {
                 const int idx = first + u * DP_THREADS;
                 at[u] = t_begin + idx / dim, ch[u] = h * dim + idx % dim;
-                zs[u] = idx < items ? z[(size_t)at[u] * z_stride + ch[u]] : 0.f;
+                zs[u] = idx < items ? z[(size_t)at[u] * z_stride + (head_decay ? h : ch[u])] : 0.f;
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 if (first + u * DP_THREADS >= items) break;
                 if (dp_slot[at[u] - t_begin] < 0) continue;
-                go[(size_t)at[u] * H * dim + ch[u]] = expf(-rate * dr_softplus(zs[u] + dt_bias[ch[u]]));
+                go[(size_t)at[u] * H * dim + ch[u]] = expf(-rate * dr_softplus(zs[u] + dt_bias[head_decay ? h : ch[u]]));
             }
         }
         for (int t = t_begin + threadIdx.x; t < t_end; t += DP_THREADS) {
@@ -310,7 +310,8 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 
 // x [tokens, >= C] of `dtype` (rows ld apart): q channels [G*dim], k channels [G*dim], v channels [H*vdim]; taps [C, K] of
 // `dtype`; b_logit [tokens, H] of `dtype` (rows b_stride apart); z float32 [tokens, H*dim] (rows z_stride apart);
-// dt_bias float32 [H*dim]; a_log float32 [H]; slot memory float32: S at `state`, the history at `hist`, both
+// dt_bias float32 [H*dim] (with `head_decay`: z [tokens, H] and dt_bias [H], one decay for all key channels of a head);
+// a_log float32 [H]; slot memory float32: S at `state`, the history at `hist`, both
 // slot_stride floats a slot.  Outputs float32, contiguous: q, k [tokens, G*dim], v, o [tokens, H*vdim], g [tokens, H*dim],
 // beta [tokens, H].
 extern "C" int dl_delta_rule(const void* x, int ld, const void* taps, int K, int dtype, const void* b_logit, int b_stride,
@@ -318,13 +319,13 @@ extern "C" int dl_delta_rule(const void* x, int ld, const void* taps, int K, int
                              const int32_t* token_seq, const int32_t* cu_new, const int32_t* slots, float* state, float* hist,
                              long slot_stride, int n_slots, float* qo, float* ko, float* vo, float* go, float* bo, float* out,
                              int n_seqs, int n_tokens, int H, int G, int dim, int vdim, float q_scale, float unit_eps,
-                             void* stream) {
+                             int head_decay, void* stream) {
     DL_REQUIRE(n_seqs >= 0 && n_tokens >= 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && n_slots > 0 && K >= 1, "delta_rule: bad sizes");
     DL_REQUIRE(H % G == 0, "delta_rule: %d heads are not a multiple of %d key heads", H, G);
     DL_REQUIRE(K <= DP_MAX_TAPS, "delta_rule: a convolution of %d taps, the kernel takes up to %d", K, DP_MAX_TAPS);
     DL_REQUIRE(dim <= DR_MAX_DIM, "delta_rule: %d key channels per head, the kernel takes up to %d", dim, DR_MAX_DIM);
     const int C = 2 * G * dim + H * vdim;
-    DL_REQUIRE(ld >= C && z_stride >= H * dim && b_stride >= H, "delta_rule: rows overlap");
+    DL_REQUIRE(ld >= C && z_stride >= (head_decay ? H : H * dim) && b_stride >= H, "delta_rule: rows overlap");
     DL_REQUIRE(dtype == DL_F32 || dtype == DL_BF16, "delta_rule: dtype %d", dtype);
     if (n_seqs == 0 || n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
@@ -339,7 +340,7 @@ extern "C" int dl_delta_rule(const void* x, int ld, const void* taps, int K, int
     e = dl_launch_dependent(delta_prepare_kernel<T, KMAX>, pgrid, dim3(DP_THREADS), smem, s, (const T*)x, ld, (const T*)taps, \
                             K, hist, slot_stride, n_slots, token_seq, cu_new, slots, (const T*)b_logit, b_stride, z,          \
                             z_stride, dt_bias, a_log, qo, ko, vo, go, bo, H, G, dim, vdim, q_scale, unit_eps,                 \
-                            single ? 1 : 0, n_tokens, per_block)
+                            single ? 1 : 0, n_tokens, per_block, head_decay)
     if (dtype == DL_F32) {
         if (K <= 4) { DP_LAUNCH(float, 4); } else if (K <= 8) { DP_LAUNCH(float, 8); } else if (K <= 16) { DP_LAUNCH(float, 16); } else { DP_LAUNCH(float, DP_MAX_TAPS); }
     } else {

@@ -2,7 +2,10 @@
 //
 //   router:  z = R x + b (float32);  the `top` largest z choose the experts, ties to the lower index;
 //            their weights are the softmax over the chosen z alone (scoring 0), or sigmoid(z) of each
-//            chosen expert as it is, not renormalised (scoring 1)
+//            chosen expert as it is, not renormalised (scoring 1), or the chosen experts' shares s of the softmax
+//            over ALL experts (scoring 2), optionally chosen by s + a correction per expert, divided by their sum
+//            (+ 1e-20) and multiplied by a constant
+//   identity experts: the experts behind the last one with matrices give back their input, y = x
 //   expert:  y = D_e act(G_e x, U_e x)       (act: one of the gatings of gating.cuh), or D_e act(U_e x)
 //            for an activation of one product; the weight multiplies y, or (a row scale) the expert's input x
 //   output:  sum over the chosen experts of weight * y   (+ an addend per token, e.g. a shared expert,
@@ -23,19 +26,23 @@
 // logits float32 [rows, E] (the router's product), bias float32 [E] or NULL.  A warp per row.
 // scoring 2: the weights are the chosen experts' shares of the softmax over ALL experts, not renormalised.  With
 // `groups` > 0 the experts lie in that many equal runs of neighbours; a run's score is its largest logit, and only the
-// experts of the `keep_groups` best runs (ties to the lower index) can be chosen.
+// experts of the `keep_groups` best runs (ties to the lower index) can be chosen.  `correction` (float32 [E] or NULL, scoring 2
+// without groups): the choice goes by share + correction, the weights stay the shares.  `normalise`: the chosen weights are
+// divided by their sum + 1e-20.  Every weight is multiplied by `weight_scale`.
 __global__ void __launch_bounds__(32 * EX_WARPS)
 route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ bias, int32_t* __restrict__ ids,
-                  float* __restrict__ weights, int rows, int E, int top, int scoring, int groups, int keep_groups) {
-    extern __shared__ float route_smem[];            // per warp: E logits, then `top` chosen values, then `groups` run scores
+                  float* __restrict__ weights, int rows, int E, int top, int scoring, int groups, int keep_groups,
+                  const float* __restrict__ correction, int normalise, float weight_scale) {
+    extern __shared__ float route_smem[];            // per warp: E logits, `top` chosen values, `groups` run scores, E shares
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * EX_WARPS + warp;
     if (row >= rows) return;                          // warps are independent below
-    float* logits = route_smem + (size_t)warp * (E + top + groups);
+    float* logits = route_smem + (size_t)warp * (E + top + groups + (correction != nullptr ? E : 0));
     float* chosen = logits + E;
     float* run_best = chosen + top;
+    float* shares = run_best + groups;                // [E], only with a correction
     float all_max = -INFINITY, all_sum = 0.f;
     for (int e = lane; e < E; e += 32) {
         logits[e] = z[(size_t)row * z_stride + e] + (bias != nullptr ? bias[e] : 0.f);
@@ -46,6 +53,13 @@ route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __rest
         all_max = dl_warp_max(all_max);
         for (int e = lane; e < E; e += 32) all_sum += expf(logits[e] - all_max);
         all_sum = dl_warp_sum(all_sum);
+        if (correction != nullptr) {                  // the choice goes by share + correction: the logits' places hold that sum
+            for (int e = lane; e < E; e += 32) {
+                shares[e] = expf(logits[e] - all_max) / all_sum;
+                logits[e] = shares[e] + correction[e];
+            }
+            __syncwarp();
+        }
     }
     if (groups > 0 && keep_groups < groups) {
         const int per = E / groups;
@@ -101,7 +115,14 @@ route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __rest
             return;
         }
         if (scoring == 2) {
-            for (int j = 0; j < top; ++j) weights[(size_t)row * top + j] = expf(chosen[j] - all_max) / all_sum;
+            float sum = 0.f;
+            for (int j = 0; j < top; ++j) {
+                const int at = ids[(size_t)row * top + j];
+                chosen[j] = correction != nullptr ? shares[at] : expf(chosen[j] - all_max) / all_sum;
+                sum += chosen[j];
+            }
+            const float f = normalise ? weight_scale / (sum + 1e-20f) : weight_scale;
+            for (int j = 0; j < top; ++j) weights[(size_t)row * top + j] = chosen[j] * f;
             return;
         }
         const float m = chosen[0];
@@ -113,18 +134,21 @@ route_topk_kernel(const float* __restrict__ z, int z_stride, const float* __rest
 
 // z float32 [rows, E], rows z_stride apart; bias float32 [E] or NULL; ids int32 [rows, top]; weights float32 [rows, top].
 extern "C" int dl_route_topk(const float* z, int z_stride, const float* bias, int32_t* ids, float* weights, int rows, int E,
-                             int top, int scoring, int groups, int keep_groups, void* stream) {
+                             int top, int scoring, int groups, int keep_groups, const float* correction, int normalise,
+                             float weight_scale, void* stream) {
     DL_REQUIRE(rows >= 0 && E > 0 && top > 0 && top <= E && z_stride >= E, "route_topk: bad sizes E=%d top=%d", E, top);
     DL_REQUIRE(scoring >= 0 && scoring <= 2, "route_topk: scoring %d (0: softmax over the chosen, 1: sigmoid, 2: softmax over all)", scoring);
     DL_REQUIRE(groups >= 0 && (groups == 0 || (E % groups == 0 && keep_groups > 0 && keep_groups <= groups &&
                                                top <= keep_groups * (E / groups))),
                "route_topk: %d experts in %d runs of which %d stay cannot give %d choices", E, groups, keep_groups, top);
-    const size_t smem = (size_t)EX_WARPS * (E + top + groups) * sizeof(float);
+    DL_REQUIRE((correction == nullptr && !normalise && weight_scale == 1.0f) || (scoring == 2 && groups == 0),
+               "route_topk: a correction, normalised weights and a scale go with the softmax over all experts, without groups");
+    const size_t smem = (size_t)EX_WARPS * (E + top + groups + (correction != nullptr ? E : 0)) * sizeof(float);
     DL_REQUIRE(smem <= 48 * 1024, "route_topk: %d experts are more than the kernel's shared memory takes", E);
     if (rows == 0) return DL_OK;
     const dim3 grid((rows + EX_WARPS - 1) / EX_WARPS), block(32 * EX_WARPS);
     cudaError_t e = dl_launch_dependent(route_topk_kernel, grid, block, smem, (cudaStream_t)stream, z, z_stride, bias, ids, weights,
-                                        rows, E, top, scoring, groups, keep_groups);
+                                        rows, E, top, scoring, groups, keep_groups, correction, normalise, weight_scale);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "route_topk: %s", cudaGetErrorString(e));
     return DL_OK;
 }
@@ -203,6 +227,10 @@ expert_gate_up_kernel(const T* __restrict__ x, int x_stride, const int32_t* __re
     const int n1 = min(ff, n0 + per_block);
     const bool ok = e >= 0 && e < E;
     const bool gated = dl_gate_is_gated(kind);
+    if (!ok) {                                       // no such expert (or one without matrices): nothing to compute
+        for (int n = n0 + threadIdx.x; n < n1; n += blockDim.x) out[(size_t)r * ff + n] = dl_from_f32<T>(0.f);
+        return;
+    }
     const T* we = w + (size_t)(ok ? e : 0) * (gated ? 2 : 1) * ff * K;
     for (int n = n0 + warp; n < n1; n += EX_WARPS) {
         const T* gr = we + (size_t)n * K;
@@ -240,13 +268,14 @@ extern "C" int dl_expert_gate_up(const void* x, int x_stride, const int32_t* ids
 
 // out[t, n] = sum_j weights[t, j] * (D_e(t,j)[n, :] . h[t * top + j, :])  (+ addend[t, n]), float32.
 // h: [tokens * top, ff] of dtype; w: [E, N, ff].  weights NULL: every weight is 1.  addend_gate (float32, one logit per
-// token, addend_gate_stride apart) or NULL: the addend is multiplied by sigmoid(logit).
+// token, addend_gate_stride apart) or NULL: the addend is multiplied by sigmoid(logit).  identity (rows identity_stride apart)
+// or NULL: a chosen id in [E, E + n_identity) is an expert that gives back its input, weight * identity[t, n].
 template <typename T>
 __global__ void __launch_bounds__(32 * EX_WARPS)
 expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, const float* __restrict__ weights,
                    const T* __restrict__ w, const float* __restrict__ addend, int addend_stride, float* __restrict__ out,
                    int top, int ff, int N, int E, int vec, int per_block, const float* __restrict__ addend_gate,
-                   int addend_gate_stride) {
+                   int addend_gate_stride, const T* __restrict__ identity, int identity_stride, int n_identity) {
     extern __shared__ float ex_h[];                  // [top][ff]
     dl_launch_dependents();
     dl_grid_dependency_wait();
@@ -266,6 +295,8 @@ expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, con
         float total = 0.f;
         for (int j = 0; j < top; ++j) {
             const int e = ids[(size_t)t * top + j];
+            if (e >= E && e < E + n_identity && identity != nullptr)
+                total += (weights != nullptr ? weights[(size_t)t * top + j] : 1.0f) * dl_to_f32<T>(identity[(size_t)t * identity_stride + n]);
             if (e < 0 || e >= E) continue;
             const T* wr = w + ((size_t)e * N + n) * ff;
             const float* hj = ex_h + (size_t)j * staged;
@@ -277,8 +308,10 @@ expert_down_kernel(const T* __restrict__ h, const int32_t* __restrict__ ids, con
 
 extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* weights, const void* w, const float* addend,
                               int addend_stride, float* out, int dtype, int tokens, int top, int ff, int N, int E,
-                              const float* addend_gate, int addend_gate_stride, void* stream) {
+                              const float* addend_gate, int addend_gate_stride, const void* identity, int identity_stride,
+                              int n_identity, void* stream) {
     DL_REQUIRE(tokens >= 0 && top > 0 && ff > 0 && N > 0 && E > 0, "expert_down: bad sizes");
+    DL_REQUIRE(identity == nullptr || (n_identity > 0 && identity_stride >= N), "expert_down: identity experts give back rows of the output's width");
     DL_REQUIRE((size_t)top * ex_staged(ff, 8) * sizeof(float) <= 96 * 1024, "expert_down: %d x %d activations are more than the kernel takes",
                top, ff);
     if (tokens == 0) return DL_OK;
@@ -291,13 +324,14 @@ extern "C" int dl_expert_down(const void* h, const int32_t* ids, const float* we
     if (dtype == DL_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<float>, grid, block, smem, s, (const float*)h, ids, weights, (const float*)w,
-                                addend, addend_stride, out, top, ff, N, E, vec, per_block, addend_gate, addend_gate_stride);
+                                addend, addend_stride, out, top, ff, N, E, vec, per_block, addend_gate, addend_gate_stride,
+                                (const float*)identity, identity_stride, n_identity);
     } else if (dtype == DL_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(expert_down_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         e = dl_launch_dependent(expert_down_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, ids, weights,
                                 (const __nv_bfloat16*)w, addend, addend_stride, out, top, ff, N, E, vec, per_block, addend_gate,
-                                addend_gate_stride);
+                                addend_gate_stride, (const __nv_bfloat16*)identity, identity_stride, n_identity);
     } else
         return dl_fail(DL_ERR_UNSUPPORTED, "expert_down: dtype %d", dtype);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_down: %s", cudaGetErrorString(e));
@@ -382,11 +416,12 @@ expert_gather_scaled_kernel(const uint4* __restrict__ x, int x_stride16, const i
 }
 
 // out[t, n] = sum_j weights[t, j] * y[place[t * top + j], n]  (+ addend[t, n]), float32; weights NULL: all 1;
-// addend_gate as in the down kernel above
+// addend_gate and identity (bfloat16 rows; ids name the chosen experts, E of them with matrices) as in the down kernel above
 __global__ void __launch_bounds__(256)
 expert_combine_kernel(const float* __restrict__ y, int y_stride, const int32_t* __restrict__ place, const float* __restrict__ weights,
                       const float* __restrict__ addend, int addend_stride, float* __restrict__ out, int top, int N,
-                      const float* __restrict__ addend_gate, int addend_gate_stride) {
+                      const float* __restrict__ addend_gate, int addend_gate_stride, const int32_t* __restrict__ ids,
+                      const __nv_bfloat16* __restrict__ identity, int identity_stride, int E, int n_identity) {
     dl_launch_dependents();
     dl_grid_dependency_wait();
     const int t = blockIdx.x;
@@ -396,6 +431,11 @@ expert_combine_kernel(const float* __restrict__ y, int y_stride, const int32_t* 
         for (int j = 0; j < top; ++j) {
             const int p = place[(size_t)t * top + j];
             if (p >= 0) total += (weights != nullptr ? weights[(size_t)t * top + j] : 1.0f) * y[(size_t)p * y_stride + n];
+            else if (identity != nullptr) {
+                const int e = ids[(size_t)t * top + j];
+                if (e >= E && e < E + n_identity)
+                    total += (weights != nullptr ? weights[(size_t)t * top + j] : 1.0f) * __bfloat162float(identity[(size_t)t * identity_stride + n]);
+            }
         }
         out[(size_t)t * N + n] = total + (addend != nullptr ? ag * addend[(size_t)t * addend_stride + n] : 0.f);
     }
@@ -430,11 +470,14 @@ extern "C" int dl_expert_gather(const void* x, int x_stride, const int32_t* plac
 
 extern "C" int dl_expert_combine(const float* y, int y_stride, const int32_t* place, const float* weights, const float* addend,
                                  int addend_stride, float* out, int tokens, int top, int N, const float* addend_gate,
-                                 int addend_gate_stride, void* stream) {
+                                 int addend_gate_stride, const int32_t* ids, const void* identity, int identity_stride, int E,
+                                 int n_identity, void* stream) {
     DL_REQUIRE(tokens >= 0 && top > 0 && N > 0 && y_stride >= N, "expert_combine: bad sizes");
+    DL_REQUIRE(identity == nullptr || (ids != nullptr && n_identity > 0 && identity_stride >= N), "expert_combine: identity experts need the ids");
     if (tokens == 0) return DL_OK;
     cudaError_t e = dl_launch_dependent(expert_combine_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, y, y_stride, place,
-                                        weights, addend, addend_stride, out, top, N, addend_gate, addend_gate_stride);
+                                        weights, addend, addend_stride, out, top, N, addend_gate, addend_gate_stride, ids,
+                                        (const __nv_bfloat16*)identity, identity_stride, E, n_identity);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "expert_combine: %s", cudaGetErrorString(e));
     return DL_OK;
 }

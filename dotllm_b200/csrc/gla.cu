@@ -9,6 +9,10 @@
 // sigmoid does not lose its digits before the root is taken), the recurrence and the norm are float32
 // whatever the storage type of q, k, v, z and g.
 //
+// A second form of the same recurrence (z NULL): one constant decay per head, alpha_t = head_decay[h] for every key
+// channel and token, with q, k and v passed through silu on their way into the scan:
+//   S_t = decay_h S_(t-1) + silu(k_t) silu(v_t)^T,   o_t = S_t^T (silu(q_t) * q_scale)
+//
 // The scan walks a sequence's new tokens in order, starting from the state that the sequence's slot
 // holds and leaving the new state there: a prompt, a part of a prompt and a single decoded token are
 // the same loop, so a position's result does not depend on how its sequence was cut into steps.  A
@@ -79,8 +83,8 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             const size_t row = (size_t)(first + tok);
             rq[l] = q[row * ld + h * dim + ch];
             rk[l] = k[row * ld + h * dim + ch];
-            rz[l] = z[row * z_stride + h * dim + ch];
-            rb[l] = z_bias[h * dim + ch];
+            rz[l] = z != nullptr ? z[row * z_stride + h * dim + ch] : 0.f;
+            rb[l] = z != nullptr ? z_bias[h * dim + ch] : z_bias[h];          // without logits: the head's constant decay
         }
 #pragma unroll
         for (int l = 0; l < GLA_VLOADS; ++l) {
@@ -100,13 +104,18 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
                 const bool live = e / PAD < count && e % PAD < dim;    // a padded channel decays to nothing and adds nothing
                 const float zz = rz[l] + rb[l];
                 const float log_sigmoid = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
-                sq[buf][e] = live ? dl_to_f32<T>(rq[l]) * q_scale : 0.f;
-                sk[buf][e] = live ? dl_to_f32<T>(rk[l]) : 0.f;
-                sa[buf][e] = live ? expf(log_sigmoid * inv_tau) : 0.f;
+                float qq = dl_to_f32<T>(rq[l]), kk = dl_to_f32<T>(rk[l]);
+                if (z == nullptr) { qq = qq / (1.0f + expf(-qq)); kk = kk / (1.0f + expf(-kk)); }
+                sq[buf][e] = live ? qq * q_scale : 0.f;
+                sk[buf][e] = live ? kk : 0.f;
+                sa[buf][e] = live ? (z != nullptr ? expf(log_sigmoid * inv_tau) : rb[l]) : 0.f;
             }
         }
 #pragma unroll
-        for (int l = 0; l < GLA_VLOADS; ++l) sv[buf][tid + GLA_THREADS * l] = dl_to_f32<T>(rv[l]);
+        for (int l = 0; l < GLA_VLOADS; ++l) {
+            const float vv = dl_to_f32<T>(rv[l]);
+            sv[buf][tid + GLA_THREADS * l] = z != nullptr ? vv : vv / (1.0f + expf(-vv));
+        }
         __syncthreads();                                        // the batch is staged; the shares of the batch before are summed
         if (first + BATCH < t1) fetch(first + BATCH, min(BATCH, t1 - first - BATCH));
 #pragma unroll 4
@@ -177,7 +186,8 @@ static int launch_scan(const void* q, const void* k, const void* v, int ld, cons
 }
 
 // q, k [tokens, H*dim] and v [tokens, H*vdim]: views with the common row stride ld (columns of one projection);
-// z float32 [tokens, H*dim] (decay logits before the bias), rows z_stride apart; z_bias float32 [H*dim];
+// z float32 [tokens, H*dim] (decay logits before the bias), rows z_stride apart; z_bias float32 [H*dim]; with z NULL
+// z_bias is float32 [H], one constant decay per head, and q, k, v pass through silu;
 // cu_new int32 [n_seqs + 1] (offsets of each sequence's tokens among the step's rows); slots int32 [n_seqs];
 // state float32 [n_slots, H, dim, vdim], read and updated; out float32 [n_tokens, H*vdim], rows out_stride apart.
 extern "C" int dl_gla_scan(const void* q, const void* k, const void* v, int ld, const float* z, int z_stride,
@@ -187,7 +197,7 @@ extern "C" int dl_gla_scan(const void* q, const void* k, const void* v, int ld, 
     DL_REQUIRE(n_seqs >= 0 && H > 0 && dim > 0 && vdim > 0 && n_slots > 0, "gla_scan: bad sizes");
     DL_REQUIRE(dim <= GLA_MAX_DIM, "gla_scan: %d key channels per head, the kernel takes up to %d", dim, GLA_MAX_DIM);
     DL_REQUIRE(tau > 0.f, "gla_scan: tau must be positive");
-    DL_REQUIRE(out_stride >= H * vdim && z_stride >= H * dim, "gla_scan: rows overlap");
+    DL_REQUIRE(out_stride >= H * vdim && (z == nullptr || z_stride >= H * dim), "gla_scan: rows overlap");
     if (n_seqs == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const bool single = n_tokens == n_seqs;          // no sequence brings less than one token: each brings exactly one

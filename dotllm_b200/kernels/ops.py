@@ -23,15 +23,20 @@ _library.register_signatures({
     "dl_gated_activation": [_P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P],
     "dl_gla_scan": [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "dl_head_norm_gate": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
-    "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "dl_route_topk": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _F, _P],
     "dl_head_rmsnorm": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
     "dl_delta_rule": [_P, _I, _P, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, ctypes.c_long, _I,
-                      _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+                      _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "dl_expert_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
-    "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+    "dl_expert_down": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P],
     "dl_expert_sort": [_P, _I, _I, _P, _P, _I, _P],
     "dl_expert_gather": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
-    "dl_expert_combine": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P, _I, _P],
+    "dl_expert_combine": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P],
+    "dl_stream_norm": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _P],
+    "dl_stream_copies": [_P, _P, _I, _I, _I, _F, _P],
+    "dl_group_rmsnorm": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _F, _P],
+    "dl_pair_norm_sum": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _F, _P],
+    "dl_scale_values": [_P, ctypes.c_longlong, _F, _P],
     "dl_unary_activation": [_P, _I, _P, _I, _I, _I, _I, _P],
     "dl_softcap": [_P, ctypes.c_longlong, _F, _P],
     "dl_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
@@ -197,6 +202,8 @@ def narrow_rows(value, ids):
     if isinstance(value, PendingProduct):
         x = resolve(value.x)
         return PendingProduct(gather_rows(x, ids, out_dtype=x.dtype), value.w, value.resident)
+    if isinstance(value, StreamWrite):
+        return value.narrowed(ids)
     if isinstance(value, NormedBranch):
         return NormedBranch(narrow_rows(value.data, ids), value.gain, value.eps,
                             None if value.extra is None else gather_rows(value.extra, ids))
@@ -266,6 +273,104 @@ def add_rows(residual, other):
         raise KernelError("add_rows: need two contiguous float32 tensors of one shape")
     _library.call("dl_add_rows", _ptr(residual), _ptr(other), residual.shape[0], residual.shape[1], _stream())
     return residual
+
+
+STREAM_NORMS = {"layernorm": 0, "rmsnorm": 1}
+
+
+class StreamWrite:
+    """A sublayer's output that has not joined a stream of copies yet: ``data`` [T, H] (a tensor or a product not yet
+    launched) is multiplied by ``scale`` (float32 [H] or None) and enters copy t with weight ``out[t]``, while the old
+    copies are mixed by ``mix`` [copies, copies] (from, to).  ``stream_norm`` takes it as its delta."""
+
+    def __init__(self, data, scale, mix, out):
+        self.data, self.scale, self.mix, self.out = data, scale, mix, out
+        self.shape = tuple(data.shape)
+
+    def narrowed(self, ids):
+        return StreamWrite(narrow_rows(self.data, ids), self.scale, self.mix, self.out)
+
+
+def stream_norm(x, copies, write, read, gain, bias, eps, out_dtype, kind="layernorm", summed=False):
+    """One pass over a stream of ``copies`` copies, x float32 [T, copies * H] (updated in place): the ``write`` of the sublayer
+    that ran last (a ``StreamWrite`` or None), then u = sum_s read[s] x_s (``read`` float32 [copies], None: every copy
+    once) and its norm (``kind`` "layernorm": (u - mean) / sqrt(var + eps) * gain + bias; "rmsnorm": u / sqrt(mean u^2 + eps)
+    * gain) in ``out_dtype``.  ``gain`` None: no norm.  ``summed``: also return u itself in float32.  Returns the normed rows,
+    or (normed, u) with ``summed``."""
+    if kind not in STREAM_NORMS:
+        raise KernelError(f"stream_norm: unknown norm {kind!r}; known: {sorted(STREAM_NORMS)}")
+    y = scale = mix = outw = None
+    if write is not None:
+        y, scale, mix, outw = resolve(write.data), write.scale, write.mix, write.out
+    _need_cuda(x, y, scale, mix, outw, read, gain, bias)
+    S = int(copies)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous() or x.shape[1] % S:
+        raise KernelError("stream_norm: the stream must be contiguous float32 [T, copies * H]")
+    T, H = x.shape[0], x.shape[1] // S
+    for t, shape, what in ((scale, (H,), "scale"), (mix, (S, S), "mix"), (outw, (S,), "out"), (read, (S,), "read"), (gain, (H,), "gain"),
+                           (bias, (H,), "bias")):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous()):
+            raise KernelError(f"stream_norm: {what} must be contiguous float32 {list(shape)}")
+    ys = 0
+    if y is not None:
+        ys = _rows_view(y, "stream_norm y")
+        if tuple(y.shape) != (T, H):
+            raise KernelError(f"stream_norm: a sublayer's output of shape {tuple(y.shape)} does not fit a stream of {(T, H)}")
+    normed = torch.empty((T, H), dtype=out_dtype, device=x.device) if gain is not None else None
+    u = torch.empty((T, H), dtype=torch.float32, device=x.device) if summed else None
+    _library.call("dl_stream_norm", _ptr(x), _ptr(y), _code(y.dtype) if y is not None else 0, ys, _ptr(scale), _ptr(mix), _ptr(outw),
+                  _ptr(read), _ptr(gain), _ptr(bias), _ptr(normed), _code(out_dtype) if normed is not None else 0, _ptr(u), T, S, H,
+                  float(eps), STREAM_NORMS[kind], _stream())
+    return (normed, u) if summed else normed
+
+
+def stream_copies(x, copies, factor=1.0):
+    """x float32 [T, H] -> float32 [T, copies * H]: every copy is x * factor."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("stream_copies: need contiguous float32 [T, H]")
+    out = torch.empty((x.shape[0], int(copies) * x.shape[1]), dtype=torch.float32, device=x.device)
+    _library.call("dl_stream_copies", _ptr(x), _ptr(out), x.shape[0], int(copies), x.shape[1], float(factor), _stream())
+    return out
+
+
+def group_rmsnorm(x, gain, width_a, width_b, eps):
+    """Columns [0, width_a) of every row divided by their root mean square (eps inside the root) and multiplied by their
+    gains, and the same for columns [width_a, width_a + width_b) on their own: queries and keys of a stacked projection,
+    each normalised over all its heads at once.  gain float32 [width_a + width_b]; x may be a column view.  Returns a new
+    tensor of x's dtype."""
+    _need_cuda(x, gain)
+    width = int(width_a) + int(width_b)
+    if x.dim() != 2 or x.shape[1] != width or gain.dtype != torch.float32 or gain.shape != (width,) or not gain.is_contiguous():
+        raise KernelError(f"group_rmsnorm: x [T, {width}] and a float32 gain per column")
+    out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+    _library.call("dl_group_rmsnorm", _ptr(x), _rows_view(x, "group_rmsnorm x"), _ptr(out), out.stride(0), _code(x.dtype), _ptr(gain),
+                  x.shape[0], int(width_a), int(width_b), float(eps), _stream())
+    return out
+
+
+def pair_norm_sum(a, b, gain_a, gain_b, eps, weight_a=0.5, weight_b=0.5):
+    """weight_a * rms(a) * gain_a + weight_b * rms(b) * gain_b per row, float32; a, b contiguous float32 [T, H]."""
+    _need_cuda(a, b, gain_a, gain_b)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.shape != b.shape or a.dim() != 2 or not a.is_contiguous() \
+            or not b.is_contiguous():
+        raise KernelError("pair_norm_sum: two contiguous float32 tensors of one shape")
+    for g in (gain_a, gain_b):
+        if g.dtype != torch.float32 or g.shape != (a.shape[1],) or not g.is_contiguous():
+            raise KernelError(f"pair_norm_sum: gains must be contiguous float32 [{a.shape[1]}]")
+    out = torch.empty_like(a)
+    _library.call("dl_pair_norm_sum", _ptr(a), _ptr(b), _ptr(gain_a), _ptr(gain_b), _ptr(out), a.shape[0], a.shape[1], float(eps),
+                  float(weight_a), float(weight_b), _stream())
+    return out
+
+
+def scale_values(values, factor):
+    """values *= factor in place (contiguous float32)."""
+    _need_cuda(values)
+    if values.dtype != torch.float32 or not values.is_contiguous():
+        raise KernelError("scale_values: need a contiguous float32 tensor")
+    _library.call("dl_scale_values", _ptr(values), values.numel(), float(factor), _stream())
+    return values
 
 
 def _add_product_scaled(residual, product, gain, eps, out_dtype):
@@ -504,22 +609,25 @@ def gated_activation(gate_up, kind, limit=0.0, alpha=1.0):
 
 
 # ------------------------------------------------------- gated linear attention
-def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_scale, tau):
+def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_scale, tau=1.0):
     """The recurrence S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_t q_scale) with
     alpha_t = sigmoid(z_t + z_bias)^(1/tau), over each sequence's new rows in order, from and into
     ``state`` float32 [slots, H, dim, vdim].  q, k [T, H*dim] and v [T, H*vdim] are column views of one
-    matrix (a common row stride) and of one dtype, z float32 [T, H*dim].  Returns o float32 [T, H*vdim]."""
+    matrix (a common row stride) and of one dtype, z float32 [T, H*dim].  With ``z`` None the decay is one constant
+    per head, ``z_bias`` float32 [H] holding it, and q, k and v pass through silu on their way into the recurrence.
+    Returns o float32 [T, H*vdim]."""
     _need_cuda(q, k, v, z, z_bias, cu_new, slots, state)
     T = q.shape[0]
     ld = _rows_view(q, "gla q")
     if _rows_view(k, "gla k") != ld or _rows_view(v, "gla v") != ld or k.shape != (T, n_heads * dim) \
-            or q.shape != k.shape or v.shape != (T, n_heads * vdim) or z.shape != k.shape:
+            or q.shape != k.shape or v.shape != (T, n_heads * vdim) or (z is not None and z.shape != k.shape):
         raise KernelError("gla_scan: q, k, v must be column views of one matrix, z [T, H*dim]")
-    if not (q.dtype == k.dtype == v.dtype) or z.dtype != torch.float32:
+    if not (q.dtype == k.dtype == v.dtype) or (z is not None and z.dtype != torch.float32):
         raise KernelError("gla_scan: q, k and v must share one dtype and z be float32")
-    zs = _rows_view(z, "gla z")
-    if z_bias.dtype != torch.float32 or z_bias.shape != (n_heads * dim,) or not z_bias.is_contiguous():
-        raise KernelError("gla_scan: the decay bias must be float32 [H*dim]")
+    zs = _rows_view(z, "gla z") if z is not None else 0
+    n_bias = n_heads * dim if z is not None else n_heads
+    if z_bias.dtype != torch.float32 or z_bias.shape != (n_bias,) or not z_bias.is_contiguous():
+        raise KernelError(f"gla_scan: the decay bias (or, without logits, the heads' decays) must be float32 [{n_bias}]")
     if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, vdim):
         raise KernelError("gla_scan: the state must be contiguous float32 [slots, H, dim, vdim]")
     _int32(cu_new, "gla cu_new")
@@ -571,7 +679,7 @@ def head_rmsnorm(x, gain_a, heads_a, dim, eps, gain_b=None, heads_b=0):
 
 # ------------------------------------------------------------------ delta rule
 def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, memory, n_heads, n_kv_heads, dim, vdim,
-               q_scale, unit_eps):
+               q_scale, unit_eps, head_decay=False):
     """The gated delta rule with a decay per key channel over each sequence's new rows in order.
 
     x [T, >= C]: the stacked projection, its first C = 2*G*dim + H*vdim columns the channels of q, k (G = ``n_kv_heads``
@@ -580,7 +688,8 @@ def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, me
     beta = sigmoid(b_logit) [T, H]; g = exp(-exp(a_log[h]) softplus(z + dt_bias)) with z float32 [T, H*dim].  Per head
     (query/key head h // (H/G)): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
     ``memory`` float32 [slots, H*dim*vdim + (K-1)*C]: per slot the states and behind them the convolution's last K - 1
-    inputs; read and updated.  Returns o float32 [T, H*vdim]."""
+    inputs; read and updated.  ``head_decay``: one decay for all key channels of a head, z float32 [T, H] and dt_bias [H].
+    Returns o float32 [T, H*vdim]."""
     _need_cuda(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, memory)
     T = x.shape[0]
     H, G = int(n_heads), int(n_kv_heads)
@@ -588,9 +697,10 @@ def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, me
     ld = _rows_view(x, "delta_rule x")
     if x.shape[1] < C or taps.shape != (C, K) or taps.dtype != x.dtype or not taps.is_contiguous():
         raise KernelError(f"delta_rule: x must hold {C} channels and the taps be [{C}, K] of its dtype")
-    if b_logit.shape != (T, H) or b_logit.dtype != x.dtype or z.shape != (T, H * dim) or z.dtype != torch.float32:
-        raise KernelError("delta_rule: b_logit [T, H] of x's dtype, z float32 [T, H*dim]")
-    for t, n, what in ((dt_bias, H * dim, "dt_bias"), (a_log, H, "a_log")):
+    n_decays = H if head_decay else H * dim
+    if b_logit.shape != (T, H) or b_logit.dtype != x.dtype or z.shape != (T, n_decays) or z.dtype != torch.float32:
+        raise KernelError(f"delta_rule: b_logit [T, H] of x's dtype, z float32 [T, {n_decays}]")
+    for t, n, what in ((dt_bias, n_decays, "dt_bias"), (a_log, H, "a_log")):
         if t.dtype != torch.float32 or t.shape != (n,) or not t.is_contiguous():
             raise KernelError(f"delta_rule: {what} must be contiguous float32 [{n}]")
     n_state = H * dim * vdim
@@ -607,7 +717,7 @@ def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, me
                   _ptr(z), _rows_view(z, "delta_rule z"), _ptr(dt_bias), _ptr(a_log), _ptr(token_seq), _ptr(cu_new), _ptr(slots),
                   memory.data_ptr(), memory.data_ptr() + 4 * n_state, memory.stride(0), memory.shape[0],
                   _ptr(qo), _ptr(ko), _ptr(vo), _ptr(go), _ptr(bo), _ptr(out), slots.numel(), T, H, G, int(dim), int(vdim),
-                  float(q_scale), float(unit_eps), _stream())
+                  float(q_scale), float(unit_eps), 1 if head_decay else 0, _stream())
     return out
 
 
@@ -615,13 +725,17 @@ def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, me
 ROUTER_SCORINGS = {"softmax_chosen": 0, "sigmoid": 1, "softmax_all": 2}
 
 
-def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False, groups=None):
+def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False, groups=None,
+               correction=None, normalise=False, weight_scale=1.0):
     """The ``top`` experts with the largest float32 logits x R^T + bias per row (ties: the lower index) and their
     weights: the softmax over the chosen logits alone (``scoring`` "softmax_chosen"), or each chosen expert's own
     sigmoid(logit), not renormalised ("sigmoid"), or its share of the softmax over all experts, not renormalised
     ("softmax_all").  ``groups`` (count, keep): the experts lie in ``count`` equal runs of neighbours, a run scores its
     largest logit, and only the experts of the ``keep`` best runs can be chosen.  ``experts``: the first that many rows of ``w_router`` are the
     experts' (default all); rows behind them ride the same product (a per-token gate, say) and only show in the logits.
+    With "softmax_all" and no groups: ``correction`` (float32 [E]) is added to the shares for the choice alone (the
+    weights stay the shares), ``normalise`` divides the chosen weights by their sum + 1e-20, and ``weight_scale``
+    multiplies them.
     Returns (ids int32 [T, top], weights float32 [T, top]), and the float32 logits [T, rows of w_router] behind them
     ``with_logits``."""
     _need_cuda(x, w_router, bias)
@@ -640,12 +754,17 @@ def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, w
     n_groups, keep_groups = (int(groups[0]), int(groups[1])) if groups else (0, 0)
     if groups and (n_groups <= 0 or E % n_groups or not 0 < keep_groups <= n_groups or top > keep_groups * (E // n_groups)):
         raise KernelError(f"route_topk: {E} experts in {n_groups} runs of which {keep_groups} stay cannot give {top} choices")
+    if correction is not None and (correction.dtype != torch.float32 or correction.shape != (E,) or not correction.is_contiguous()):
+        raise KernelError(f"route_topk: the correction must be float32 [{E}]")
+    if (correction is not None or normalise or float(weight_scale) != 1.0) and (scoring != "softmax_all" or groups):
+        raise KernelError("route_topk: a correction, normalised weights and a scale go with 'softmax_all' without groups")
     T = x.shape[0]
     z = linear(x, w_router, out_dtype=torch.float32, resident=True)         # float32 accumulation, float32 logits
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
     _library.call("dl_route_topk", _ptr(z), z.stride(0) if T > 1 else rows_w, _ptr(bias), _ptr(ids), _ptr(weights), T, E, top,
-                  ROUTER_SCORINGS[scoring], n_groups, keep_groups, _stream())
+                  ROUTER_SCORINGS[scoring], n_groups, keep_groups, _ptr(correction), 1 if normalise else 0, float(weight_scale),
+                  _stream())
     return (ids, weights, z) if with_logits else (ids, weights)
 
 
@@ -691,10 +810,22 @@ def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0, row_scale=None
     return out
 
 
-def expert_down(h, ids, weights, w_down, addend=None, addend_gate=None):
+def _identity(identity, T, N, dtype, what):
+    """(rows, row stride, count) of the input that identity experts give back, after checking it."""
+    if identity is None:
+        return None, 0, 0
+    rows, count = identity
+    if count <= 0 or rows.dtype != dtype or rows.shape != (T, N):
+        raise KernelError(f"{what}: identity experts give back rows [T, N] of the experts' dtype")
+    return rows, _rows_view(rows, what + " identity"), int(count)
+
+
+def expert_down(h, ids, weights, w_down, addend=None, addend_gate=None, identity=None):
     """out[t] = sum_j weights[t, j] * D_e(t,j) h[t*top + j]  (+ addend[t]), float32 [T, N].  h [T*top, ff];
     w_down [E, N, ff] of h's dtype; weights float32 [T, top] or None (all 1); addend float32 [T, N] (rows contiguous)
-    or None; ``addend_gate`` float32, one logit per token (column 0 of a [T, n] view): the addend times its sigmoid."""
+    or None; ``addend_gate`` float32, one logit per token (column 0 of a [T, n] view): the addend times its sigmoid.
+    ``identity`` (x [T, N] of h's dtype, n): ids E .. E + n - 1 name experts without matrices that give back their input,
+    weight * x[t]."""
     _need_cuda(h, ids, weights, w_down, addend, addend_gate)
     _int32(ids, "expert ids")
     T, top = ids.shape
@@ -704,9 +835,10 @@ def expert_down(h, ids, weights, w_down, addend=None, addend_gate=None):
         raise KernelError("expert_down: h [T*top, ff], ids and float32 weights [T, top], matrices [E, N, ff] of h's dtype")
     E, N, ff = w_down.shape
     astride, gstride = _addend(addend, addend_gate, T, N, "expert_down")
+    irows, istride, icount = _identity(identity, T, N, h.dtype, "expert_down")
     out = torch.empty((T, N), dtype=torch.float32, device=h.device)
     _library.call("dl_expert_down", _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_down), _ptr(addend), astride, _ptr(out),
-                  _code(h.dtype), T, top, ff, N, E, _ptr(addend_gate), gstride, _stream())
+                  _code(h.dtype), T, top, ff, N, E, _ptr(addend_gate), gstride, _ptr(irows), istride, icount, _stream())
     return out
 
 
@@ -725,13 +857,13 @@ def experts_grouped_takes(x, ids, w_gate_up, w_down):
 
 
 def experts_grouped(x, ids, weights, w_gate_up, w_down, kind, limit=0.0, alpha=1.0, addend=None, row_scale=None,
-                    addend_gate=None):
+                    addend_gate=None, identity=None):
     """The same result as ``expert_gate_up`` followed by ``expert_down``, for many rows: the (token, choice) rows are
     sorted by expert on the device, each expert's run padded to whole tiles, and the two products run on the tensor
     cores (tcgen05) with the gating in the first one's epilogue; a last kernel sums every token's choices with
     their weights (and the addend).  Shapes depend only on the step's sizes, never on the choice.  ``weights`` None,
     ``row_scale``, ``addend_gate`` and activations of one product as in those two (the row scale is applied as the rows
-    are gathered, the activation in the first product's epilogue)."""
+    are gathered, the activation in the first product's epilogue); ``identity`` as in ``expert_down``."""
     _need_cuda(x, ids, weights, w_gate_up, w_down, addend, row_scale, addend_gate)
     _int32(ids, "expert ids")
     T, top = ids.shape
@@ -755,9 +887,10 @@ def experts_grouped(x, ids, weights, w_gate_up, w_down, kind, limit=0.0, alpha=1
     _library.call("dl_gemm_tc_grouped_bf16", _ptr(h), ff, _ptr(w_down), _ptr(y), 0, N, tiles * EXPERT_TILE, N, ff, E,
                   _ptr(tile_expert), 0, 0, 0.0, 0.0, 0, status, _stream())
     astride, gstride = _addend(addend, addend_gate, T, N, "experts_grouped")
+    irows, istride, icount = _identity(identity, T, N, torch.bfloat16, "experts_grouped")
     out = torch.empty((T, N), dtype=torch.float32, device=dev)
     _library.call("dl_expert_combine", _ptr(y), N, _ptr(place), _ptr(weights), _ptr(addend), astride, _ptr(out), T, top, N,
-                  _ptr(addend_gate), gstride, _stream())
+                  _ptr(addend_gate), gstride, _ptr(ids), _ptr(irows), istride, E, icount, _stream())
     return out
 
 

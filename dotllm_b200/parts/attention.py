@@ -14,8 +14,18 @@ sigmoid of its logit, before the output projection; the gate's rows ride the sta
 that reads another execution's keys and values (the schedule's ``cache_of``: such a layer has no key and value
 projections, ``own_kv`` False); values that are the keys as projected, before any norm or rotation (``values`` "keys": no
 value projection); an RMS norm of every query and key head before the rotation, with one gain for the queries and one for
-the keys (``qk_norm``); a window that keeps a sequence's first tokens visible (``keep_first``); and a learned number per
-head in the softmax's denominator, a sink without key or value (``sink``).
+the keys (``qk_norm``), or an RMS norm over the whole query projection and over the whole key projection, all heads at once,
+with a gain per channel (``qk_norm`` with ``over`` "projection"); a window that keeps a sequence's first tokens visible
+(``keep_first``); a learned number per head in the softmax's denominator, a sink without key or value (``sink``), or a sink
+of score zero without a tensor (``sink`` "zero": one is added to the denominator); and a rotation that pairs channel 2i
+with 2i + 1 (``pairing`` "interleaved").
+
+Interleaved pairs on kernels that pair channel i with i + r/2.  Scores do not change when the channels of q and k are
+permuted alike, so for a rotation of the first r channels in interleaved pairs the rows of the q and k projections (and
+the gains of a norm over the whole projection, which does not care about the order either) are reordered once, when the
+weights are bound: within each head the even channels of the first r come first, then the odd ones, then the rest.  The
+cache holds the keys in that order; a layer that reads another's cache has the same rotation and orders its queries the
+same way.
 
 Keys and values of different widths on the tensor cores.  The tensor-core attention kernels take one width for keys
 and values (32, 64, 96 or 128).  In a bfloat16 run a mixer with these options whose widths differ, or are equal and none of
@@ -60,7 +70,10 @@ class AttentionMixer(Mixer):
     ``o``, ``gate`` and the bias suffix ``bias`` (appended to a projection's name); optional ``values`` ("own", or "keys":
     v is k as projected, there is no value projection and ``value_dim`` is ``head_dim``), ``qk_norm`` ({"eps"}: tensors
     ``q_norm``, ``k_norm`` [head_dim]), ``keep_first`` (with a window: that many first tokens of a sequence stay visible) and
-    ``sink`` (True: tensor ``sink`` [n_heads], exp(sink_h) joins head h's softmax denominator)."""
+    ``sink`` (True: tensor ``sink`` [n_heads], exp(sink_h) joins head h's softmax denominator; "zero": no tensor, every
+    head's denominator gets exp(0) = 1 more); ``qk_norm`` may carry ``over`` "projection" (one RMS over all the query
+    channels of a token and one over all its key channels, tensors ``q_norm`` [n_heads * head_dim], ``k_norm``
+    [n_kv_heads * head_dim]); ``pairing`` ("half", or "interleaved": the rotation pairs channel 2i with 2i + 1)."""
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
              "gate": "g_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
@@ -101,7 +114,14 @@ class AttentionMixer(Mixer):
             raise ConfigError("attention: values that are the keys have the keys' width and no biases")
         qk_norm = params.get("qk_norm")
         self.qk_norm_eps = float(qk_norm["eps"]) if qk_norm else None
+        self.qk_norm_over = str(qk_norm.get("over", "head")) if qk_norm else None
+        if self.qk_norm_over not in (None, "head", "projection"):
+            raise ConfigError(f"attention: a query/key norm runs over a 'head' or the 'projection', not {self.qk_norm_over!r}")
         self.sink = bool(params.get("sink", False))
+        self.zero_sink = params.get("sink") == "zero"
+        self.pairing = str(params.get("pairing", "half"))
+        if self.pairing not in ("half", "interleaved"):
+            raise ConfigError(f"attention: rotation pairs are 'half' or 'interleaved', not {self.pairing!r}")
         self.keep_first = int(params.get("keep_first") or 0)
         if self.keep_first < 0 or (self.keep_first and not self.window):
             raise ConfigError("attention: kept first tokens need a window (and cannot be negative)")
@@ -113,9 +133,10 @@ class AttentionMixer(Mixer):
         self.o_dim = self.n_heads * self.value_dim
         # the reference's block as it is (one matrix of q, k and v rows, nothing added): its fused paths apply
         self.plain = not self.bias and self.gate is None and self.value_dim == self.head_dim and self.own_kv \
-            and self.values == "own" and self.qk_norm_eps is None and not self.sink and not self.keep_first
+            and self.values == "own" and self.qk_norm_eps is None and not self.sink and not self.keep_first \
+            and params.get("pairing", "half") == "half"
         # heads keep their own width and channel order where a norm runs over them or the keys double as values
-        as_stored = self.values == "keys" or self.qk_norm_eps is not None
+        as_stored = self.values == "keys" or self.qk_norm_eps is not None or params.get("pairing") == "interleaved"
         self.w_qkv = None
         self.w_o = None
         self.biases = None
@@ -134,6 +155,11 @@ class AttentionMixer(Mixer):
         self.rotation = None if fused is None else (self._wide_tables(fused[0], fused[1], rd, self.lay_k) + (self.lay_k,)
                                                     if self.spread else fused)
         self.spread_order = self._spread_order(rd, self.lay_k) if self.spread else None
+        if self.pairing == "interleaved" and rd:
+            if self.spread:
+                raise ConfigError("attention: interleaved pairs go with heads kept at their stored width")
+            # new channel -> old channel of a head: pairs (2i, 2i + 1) become pairs (i, i + rd/2)
+            self.spread_order = list(range(0, rd, 2)) + list(range(1, rd, 2)) + list(range(rd, self.lay_k))
 
     TENSOR_CORE_WIDTHS = (32, 64, 96, 128)      # kernels.attention_fast.DECODE_HEAD_DIMS
 
@@ -193,10 +219,11 @@ class AttentionMixer(Mixer):
         if self.gate:
             specs[n["gate"]] = WeightSpec((self.n_heads, h), init=("normal", 0.1))
         if self.qk_norm_eps is not None:
-            specs[n["q_norm"]] = WeightSpec((self.head_dim,), "precise", ("one_plus_uniform", 0.1))
+            whole = self.qk_norm_over == "projection"
+            specs[n["q_norm"]] = WeightSpec((self.q_dim if whole else self.head_dim,), "precise", ("one_plus_uniform", 0.1))
             if self.own_kv:
-                specs[n["k_norm"]] = WeightSpec((self.head_dim,), "precise", ("one_plus_uniform", 0.1))
-        if self.sink:
+                specs[n["k_norm"]] = WeightSpec((self.kv_dim if whole else self.head_dim,), "precise", ("one_plus_uniform", 0.1))
+        if self.sink and not self.zero_sink:
             specs[n["sink"]] = WeightSpec((self.n_heads,), "precise", ("normal", 1.0))
         specs[n["o"]] = WeightSpec((h, self.o_dim))
         return specs
@@ -218,10 +245,19 @@ class AttentionMixer(Mixer):
                 rows.append(torch.zeros((pad, self.hidden_size), dtype=rows[0].dtype, device=rows[0].device))
         self.w_qkv = torch.cat(rows, dim=0).contiguous()
         self.w_o = self._widen(tensors[n["o"]], H, vd, lv, dim=1).contiguous()
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_over == "projection":
+            # one gain per channel of the projection: they follow their channels into the kernels' order
+            self.q_gain = self._reorder(tensors[n["q_norm"]], H).contiguous()
+            self.k_gain = self._reorder(tensors[n["k_norm"]], G).contiguous() if self.own_kv else None
+            self.qk_gain = torch.cat([self.q_gain, self.k_gain]).contiguous() if self.own_kv else self.q_gain
+        elif self.qk_norm_eps is not None:
+            if self.spread_order is not None:
+                raise ConfigError("attention: a gain shared by the heads does not follow reordered channels")
             self.q_gain = tensors[n["q_norm"]].contiguous()
             self.k_gain = tensors[n["k_norm"]].contiguous() if self.own_kv else None
-        if self.sink:
+        if self.zero_sink:
+            self.sinks = torch.zeros((H,), dtype=torch.float32, device=self.w_qkv.device)
+        elif self.sink:
             self.sinks = tensors[n["sink"]].contiguous()
         if self.bias:
             self.biases = (self._reorder(self._widen(tensors[n["q_bias"]], H, hd, lk), H).contiguous(),
@@ -255,7 +291,13 @@ class AttentionMixer(Mixer):
         elif self.own_kv:
             k, v, at = y[:, at:at + kvd], y[:, at + kvd:at + kvd + vw], at + kvd + vw
         g = y[:, at:at + self.n_heads] if self.gate else None
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_over == "projection":
+            if self.own_kv:
+                normed = ops.group_rmsnorm(y[:, :qd + kvd], self.qk_gain, qd, kvd, self.qk_norm_eps)
+                q, k = normed[:, :qd], normed[:, qd:]
+            else:
+                q = ops.group_rmsnorm(q, self.qk_gain, qd, 0, self.qk_norm_eps)
+        elif self.qk_norm_eps is not None:
             if self.own_kv:
                 normed = ops.head_rmsnorm(y[:, :qd + kvd], self.q_gain, self.n_heads, lk, self.qk_norm_eps, self.k_gain, self.n_kv_heads)
                 q, k = normed[:, :qd], normed[:, qd:]

@@ -13,6 +13,7 @@ Kinds are registered by name:
     register_norm("rmsnorm", RmsNorm)
     register_position_encoding("rotary", RotaryEncoding)
     register_arrangement("pre_norm", PreNormBlock)
+    register_connection("stream_copies", StreamConnection)
 
 and a ``PartSpec(kind, params, prefix)`` picks one per layer.
 """
@@ -41,7 +42,7 @@ class WeightSpec:
     role "precise": used in 32-bit arithmetic (norm gains); widened to / kept in float32.
     role "index": integer table; kept as int32.
     ``init`` says how the random-weights mode fills it: ("normal", std), ("ones",),
-    ("one_plus_uniform", a) or ("zeros",).
+    ("one_plus_uniform", a), ("zeros",), ("uniform", lo, hi) or ("eye_plus_normal", std) (a square matrix around the identity).
     ``free_dims``: dimensions whose size only the stored tensor gives (a rank that no configuration
     key names); ``shape`` holds the size the random-weights mode uses there, a checkpoint may hold any.
     """
@@ -170,6 +171,8 @@ class Mixer(Part):
     """Mixes information across the tokens of a sequence (attention, recurrence, ...)."""
 
     def cache_need(self) -> Optional[CacheNeed]:
+        """None, one CacheNeed, or a tuple of them for a mixer made of several that each keep something (``cache_view``
+        is then a tuple of views in the same order)."""
         return None
 
     def forward(self, x, step, cache_view):
@@ -180,6 +183,22 @@ class Mixer(Part):
 
         ``step`` is the engine's StepContext (token -> sequence map, positions, lengths);
         ``cache_view`` gives this execution's storage (``LayerCacheView``) or None."""
+        raise NotImplementedError
+
+
+class Connection(Part):
+    """How a sublayer meets the residual stream: what its norm reads from the stream, and how its output joins it.  The
+    ordinary residual sum is the simplest one; a stream kept as several copies that every sublayer reads and writes with
+    weights of its own is another."""
+
+    def read(self, norm, stream, pending):
+        """Apply ``pending`` (what ``write`` of the sublayer before returned, or None) to the float32 ``stream`` in place,
+        then return what this sublayer's ``norm`` makes of the stream, in the run dtype."""
+        raise NotImplementedError
+
+    def write(self, data):
+        """``data`` (the sublayer's output, possibly a product not yet launched) as something the next ``read``, or the
+        model's last norm, adds to the stream."""
         raise NotImplementedError
 
 
@@ -223,7 +242,7 @@ class Arrangement:
 
 
 _REGISTRIES = {"mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "arrangement": {},
-               "embedding": {}, "head": {}}
+               "embedding": {}, "head": {}, "connection": {}}
 
 
 def _register(family, kind, cls):
@@ -251,6 +270,10 @@ def register_arrangement(kind, cls):
     return _register("arrangement", kind, cls)
 
 
+def register_connection(kind, cls):
+    return _register("connection", kind, cls)
+
+
 def register_embedding(kind, cls):
     return _register("embedding", kind, cls)
 
@@ -266,7 +289,7 @@ def registered(family):
 
 def _ensure_builtin():
     from . import (norms, rotary, attention, feed_forward, blocks, embedding, linear_attention,  # noqa: F401
-                   latent_attention, experts, delta_rule)
+                   latent_attention, experts, delta_rule, connections, paired)
 
 
 def make_part(family, spec, hidden_size, runtime):

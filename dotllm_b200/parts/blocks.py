@@ -75,6 +75,29 @@ class ParallelBlock(Arrangement):
         return residual, self.feed_forward.forward(n)
 
 
+class ConnectedBlock(Arrangement):
+    """Pre-norm sublayers that meet the stream through connections of their own (``parts.connections``): what a
+    sublayer's norm reads and how its output joins are the connection's business, so the stream may be several copies
+    with read, write and mixing weights per sublayer, or one stream with a gain on every branch.  A sublayer's output is
+    handed on unadded; the next read (the next layer's, or the model's last norm) adds it.  The feed-forward with its norm
+    and connection may be absent."""
+    needs = ("mixer_norm", "mixer", "mixer_connection")
+    narrows = True
+
+    def forward(self, residual, pending, step, cache_view, keep_rows=None):
+        n = self.mixer_connection.read(self.mixer_norm, residual, pending)
+        branch = self.mixer_connection.write(self.mixer.forward(n, step, cache_view))   # every token: the cache needs them all
+        if keep_rows is not None:
+            from ..kernels import ops
+            residual = ops.gather_rows(residual, keep_rows)
+            branch = ops.narrow_rows(branch, keep_rows)
+        if "feed_forward" not in self.parts:
+            return residual, branch
+        n = self.feed_forward_connection.read(self.feed_forward_norm, residual, branch)
+        return residual, self.feed_forward_connection.write(self.feed_forward.forward(n))
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("connected", ConnectedBlock)
 register_arrangement("parallel", ParallelBlock)
 register_arrangement("sandwich_norm", SandwichNormBlock)

@@ -14,12 +14,16 @@ from .base import Part, WeightSpec, register_embedding, register_head
 
 
 class TokenEmbedding(Part):
-    """params: ``vocab_size``; optional ``tensor`` (the table's local name, default "weight") and ``init_std``."""
+    """params: ``vocab_size``; optional ``tensor`` (the table's local name, default "weight"), ``init_std``, ``scale``
+    (h[t] = E[token[t]] * scale, the product taken in float32) and ``copies`` (S > 1: the stream starts as S copies of that
+    row side by side, float32 [T, S * H], for layers that keep a stream of copies)."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
         self.vocab_size = int(params["vocab_size"])
         self.tensor_name = str(params.get("tensor", "weight"))
+        self.scale = float(params.get("scale", 1.0))
+        self.copies = int(params.get("copies") or 1)
         self.table = None
 
     def weight_specs(self):
@@ -33,7 +37,10 @@ class TokenEmbedding(Part):
         """The step's tokens (``step.tokens`` int32 [T]) -> float32 [T, H]: the start of the residual
         stream.  An embedding gets the whole StepContext: one that also encodes positions reads
         ``step.token_pos``."""
-        return ops.gather_rows(self.table, step.tokens)
+        rows = ops.gather_rows(self.table, step.tokens)
+        if self.copies == 1 and self.scale == 1.0:
+            return rows
+        return ops.stream_copies(rows, self.copies, self.scale)
 
 
 class TokenPositionEmbedding(Part):
@@ -63,7 +70,8 @@ class TokenPositionEmbedding(Part):
 
 
 class LinearHead(Part):
-    """params: ``vocab_size``; optional ``softcap`` (c > 0: logits become c tanh(logits / c)) and ``tensor`` (the
+    """params: ``vocab_size``; optional ``softcap`` (c > 0: logits become c tanh(logits / c)), ``scale`` (the logits are
+    multiplied by it, in float32, before any cap) and ``tensor`` (the
     local name of the matrix, default "weight"; "" when the prefix is the whole name).  Whether its matrix is the
     embedding table is the model description's business (``ModelSpec.shared_weights``): the part is handed a
     [vocab, hidden] matrix either way."""
@@ -72,6 +80,7 @@ class LinearHead(Part):
         super().__init__(params, hidden_size, runtime)
         self.vocab_size = int(params["vocab_size"])
         self.softcap = float(params.get("softcap") or 0.0)
+        self.scale = float(params.get("scale", 1.0))
         self.tensor_name = str(params.get("tensor", "weight"))
         self.weight = None
 
@@ -90,6 +99,8 @@ class LinearHead(Part):
     def forward(self, x):
         """[R, H] in the run dtype -> float32 logits [R, vocab]."""
         logits = ops.linear(x, self.weight, out_dtype=torch.float32, resident=True)
+        if self.scale != 1.0:
+            logits = ops.scale_values(logits, self.scale)
         return ops.softcap(logits, self.softcap) if self.softcap > 0 else logits
 
 

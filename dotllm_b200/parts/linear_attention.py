@@ -88,4 +88,72 @@ class GatedLinearAttentionMixer(Mixer):
         return ops.linear(y, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
 
 
+class DecayedLinearAttentionMixer(Mixer):
+    """Linear attention whose state decays by one constant per head (lightning attention):
+
+        q, k, v = silu(Wq x), silu(Wk x), silu(Wv x)          (heads x dim, heads x dim, heads x vdim)
+        S_t = decay_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t    (no other scale)
+        y   = Wo (rms(concat_heads(o_t)) * gain * sigmoid(Wg x))   (one RMS over all heads' outputs together)
+
+    The four projections that read x are one stacked matrix; the scan is the gated linear attention's kernel in its
+    constant-decay form (silu inside, float32 state per slot, a sequence's new tokens walked in order from the cached
+    state); the norm over the concatenated heads is the per-head norm kernel with one head as wide as all.
+
+    params: ``n_heads``, ``key_dim``, ``value_dim`` (per head), ``decay`` (one number in (0, 1] per head), ``eps``; optional
+    ``tensors``: local names of q, k, v, gate, out, norm."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "norm": "norm"}
+    ROW_STEP = 16
+
+    def __init__(self, params, hidden_size, runtime):
+        super().__init__(params, hidden_size, runtime)
+        self.n_heads = int(params["n_heads"])
+        self.key_dim = int(params["key_dim"])
+        self.value_dim = int(params["value_dim"])
+        self.eps = float(params["eps"])
+        decay = [float(d) for d in params["decay"]]
+        if min(self.n_heads, self.key_dim, self.value_dim) <= 0 or len(decay) != self.n_heads or not all(0.0 <= d <= 1.0 for d in decay):
+            raise ConfigError("decayed linear attention: positive sizes and one decay in [0, 1] per head")
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        self.names = dict(self.NAMES, **(params.get("tensors") or {}))
+        self.k_width = self.n_heads * self.key_dim
+        self.v_width = self.n_heads * self.value_dim
+        self.w_in = self.norm_gain = self.w_o = None
+
+    def weight_specs(self):
+        h, n = self.hidden_size, self.names
+        return {n["q"]: WeightSpec((self.k_width, h)),
+                n["k"]: WeightSpec((self.k_width, h)),
+                n["v"]: WeightSpec((self.v_width, h)),
+                n["gate"]: WeightSpec((self.v_width, h)),
+                n["out"]: WeightSpec((h, self.v_width)),
+                n["norm"]: WeightSpec((self.v_width,), "precise", ("one_plus_uniform", 0.1))}
+
+    def bind(self, tensors):
+        n = self.names
+        rows = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]], tensors[n["gate"]]]
+        pad = -sum(r.shape[0] for r in rows) % self.ROW_STEP
+        if pad:
+            rows.append(torch.zeros((pad, self.hidden_size), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.norm_gain = tensors[n["norm"]].contiguous()
+        self.w_o = tensors[n["out"]].contiguous()
+
+    def weight_bytes(self):
+        return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size()
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.n_heads, self.key_dim, self.value_dim), state_dtype=torch.float32)
+
+    def forward(self, x, step, cache_view):
+        kw, vw = self.k_width, self.v_width
+        proj = ops.linear(x, self.w_in, resident=True)
+        q, k, v, gate = proj[:, :kw], proj[:, kw:2 * kw], proj[:, 2 * kw:2 * kw + vw], proj[:, 2 * kw + vw:2 * kw + 2 * vw]
+        o = ops.gla_scan(q, k, v, None, self.decay, step.cu_new, cache_view.slots, cache_view.state, self.n_heads, self.key_dim,
+                         self.value_dim, 1.0)
+        y = ops.head_norm_gate(o, gate, self.norm_gain, 1, vw, self.eps, self.runtime.dtype, gate="sigmoid")
+        return ops.linear(y, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
+
+
 register_mixer("gated_linear_attention", GatedLinearAttentionMixer)
+register_mixer("decayed_linear_attention", DecayedLinearAttentionMixer)

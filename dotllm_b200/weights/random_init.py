@@ -38,6 +38,12 @@ def random_tensor(name, spec, seed, device="cpu"):
     if kind == "one_plus_uniform":
         a = float(spec.init[1])
         return 1.0 + (torch.rand(shape, generator=gen, dtype=torch.float32, device=device) * 2.0 - 1.0) * a
+    if kind == "uniform":
+        lo, hi = float(spec.init[1]), float(spec.init[2])
+        return lo + torch.rand(shape, generator=gen, dtype=torch.float32, device=device) * (hi - lo)
+    if kind == "eye_plus_normal":
+        return torch.eye(shape[0], shape[1], dtype=torch.float32, device=device) + \
+            torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * float(spec.init[1])
     raise ValueError(f"unknown init {spec.init!r} for tensor {name!r}")
 
 

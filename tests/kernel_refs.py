@@ -68,12 +68,17 @@ def gated_activation(gate_up, kind, limit=0.0, alpha=1.0):
     return y.to(gate_up.dtype)
 
 
-def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_scale, tau):
+def gla_scan(q, k, v, z, z_bias, cu_new, slots, state, n_heads, dim, vdim, q_scale, tau=1.0):
     T = q.shape[0]
     out = torch.zeros((T, n_heads * vdim), dtype=torch.float32, device=q.device)
-    alpha = torch.exp(torch.nn.functional.logsigmoid(z.to(torch.float32) + z_bias) / tau).view(T, n_heads, dim)
-    qf = q.to(torch.float32).view(T, n_heads, dim) * q_scale
-    kf, vf = k.to(torch.float32).view(T, n_heads, dim), v.to(torch.float32).view(T, n_heads, vdim)
+    qf, kf, vf = q.to(torch.float32), k.to(torch.float32), v.to(torch.float32)
+    if z is None:                                           # one constant decay per head; silu on the way in
+        alpha = z_bias.view(1, n_heads, 1).expand(T, n_heads, dim)
+        qf, kf, vf = (t * torch.sigmoid(t) for t in (qf, kf, vf))
+    else:
+        alpha = torch.exp(torch.nn.functional.logsigmoid(z.to(torch.float32) + z_bias) / tau).view(T, n_heads, dim)
+    qf = qf.reshape(T, n_heads, dim) * q_scale
+    kf, vf = kf.reshape(T, n_heads, dim), vf.reshape(T, n_heads, vdim)
     for b in range(slots.numel()):
         S = state[int(slots[b])]
         for t in range(int(cu_new[b]), int(cu_new[b + 1])):
@@ -99,7 +104,7 @@ def head_rmsnorm(x, gain_a, heads_a, dim, eps, gain_b=None, heads_b=0):
 
 
 def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, memory, n_heads, n_kv_heads, dim, vdim,
-               q_scale, unit_eps):
+               q_scale, unit_eps, head_decay=False):
     """Sequence by sequence, token by token, from and into the slot's memory (states, then the convolution's history)."""
     T, H, G = x.shape[0], n_heads, n_kv_heads
     C, K = taps.shape
@@ -124,12 +129,58 @@ def delta_rule(x, taps, b_logit, z, dt_bias, a_log, token_seq, cu_new, slots, me
             k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
             q, k = q.repeat_interleave(H // G, dim=0), k.repeat_interleave(H // G, dim=0)
             beta = torch.sigmoid(b_logit[t].to(torch.float32))
-            g = torch.exp(-torch.exp(a_log)[:, None] * torch.nn.functional.softplus((z[t] + dt_bias).view(H, dim)))
+            zt = (z[t] + dt_bias).view(H, 1).expand(H, dim) if head_decay else (z[t] + dt_bias).view(H, dim)
+            g = torch.exp(-torch.exp(a_log)[:, None] * torch.nn.functional.softplus(zt))
             S.mul_(g[:, :, None])
             u = beta[:, None] * (v - torch.einsum("hdv,hd->hv", S, k))
             S.add_(k[:, :, None] * u[:, None, :])
             out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
     return out
+
+
+class StreamWrite:
+    def __init__(self, data, scale, mix, out):
+        self.data, self.scale, self.mix, self.out = data, scale, mix, out
+        self.shape = tuple(data.shape)
+
+    def narrowed(self, ids):
+        return StreamWrite(self.data[ids.long()], self.scale, self.mix, self.out)
+
+
+def stream_norm(x, copies, write, read, gain, bias, eps, out_dtype, kind="layernorm", summed=False):
+    T, S = x.shape[0], int(copies)
+    xs = x.view(T, S, -1)
+    if write is not None:
+        y = write.data.to(torch.float32) * (write.scale if write.scale is not None else 1.0)
+        xs.copy_(torch.einsum("sr,tsh->trh", write.mix, xs.clone()) + write.out[None, :, None] * y[:, None, :])
+    u = xs.sum(dim=1) if read is None else torch.einsum("s,tsh->th", read, xs)
+    normed = None
+    if gain is not None:
+        if kind == "layernorm":
+            d = u - u.mean(dim=-1, keepdim=True)
+            normed = d / torch.sqrt((d * d).mean(dim=-1, keepdim=True) + eps) * gain + (bias if bias is not None else 0.0)
+        else:
+            normed = _rms(u, eps) * gain
+        normed = normed.to(out_dtype)
+    return (normed, u) if summed else normed
+
+
+def stream_copies(x, copies, factor=1.0):
+    return (x * factor).repeat(1, int(copies))
+
+
+def group_rmsnorm(x, gain, width_a, width_b, eps):
+    xf = x.to(torch.float32)
+    parts = [_rms(xf[:, :width_a], eps)] + ([_rms(xf[:, width_a:width_a + width_b], eps)] if width_b else [])
+    return (torch.cat(parts, dim=1) * gain).to(x.dtype)
+
+
+def pair_norm_sum(a, b, gain_a, gain_b, eps, weight_a=0.5, weight_b=0.5):
+    return weight_a * _rms(a, eps) * gain_a + weight_b * _rms(b, eps) * gain_b
+
+
+def scale_values(values, factor):
+    return values.mul_(factor)
 
 
 def unary_activation(x, kind):
@@ -152,12 +203,15 @@ def head_gate(o, gate, n_heads, width):
     return o
 
 
-def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False, groups=None):
+def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, with_logits=False, groups=None,
+               correction=None, normalise=False, weight_scale=1.0):
     logits = x.to(torch.float32) @ w_router.to(torch.float32).T
     z = logits[:, :experts] if experts is not None else logits
     if bias is not None:
         z = z + bias
     share = torch.softmax(z, dim=-1)                        # over every expert, before any is ruled out
+    if correction is not None:                              # the choice goes by share + correction
+        z = share + correction
     if groups:
         count, keep = groups
         left = z.reshape(z.shape[0], count, -1).max(dim=-1).values
@@ -178,6 +232,9 @@ def route_topk(x, w_router, bias, top, scoring="softmax_chosen", experts=None, w
         z = z.scatter(1, at[:, None], float("-inf"))
     if scoring == "softmax_all":
         weights = torch.gather(share, 1, ids.long())
+        if normalise:
+            weights = weights / (weights.sum(dim=-1, keepdim=True) + 1e-20)
+        weights = weights * weight_scale
     else:
         weights = torch.sigmoid(vals) if scoring == "sigmoid" else torch.softmax(vals, dim=-1)
     return (ids, weights, logits) if with_logits else (ids, weights)
@@ -187,19 +244,25 @@ def expert_gate_up(x, ids, w_gate_up, kind, limit=0.0, alpha=1.0, row_scale=None
     T, top = ids.shape
     act = (lambda y: unary_activation(y, kind)) if kind == "relu2" else (lambda y: gated_activation(y, kind, limit, alpha))
     scale = (lambda t, j: float(row_scale[t, j])) if row_scale is not None else (lambda t, j: 1.0)
-    rows = [act((x[t:t + 1].to(torch.float32) * scale(t, j)) @ w_gate_up[int(ids[t, j])].to(torch.float32).T)[0]
+    E = w_gate_up.shape[0]                                  # an id beyond the matrices (an identity expert) gives zeros here
+    rows = [act((x[t:t + 1].to(torch.float32) * scale(t, j)) @ w_gate_up[int(ids[t, j]) % E].to(torch.float32).T)[0] * (int(ids[t, j]) < E)
             for t in range(T) for j in range(top)]
     width = w_gate_up.shape[1] if kind == "relu2" else w_gate_up.shape[1] // 2
     return torch.stack(rows).to(x.dtype) if rows else torch.zeros((0, width), dtype=x.dtype)
 
 
-def expert_down(h, ids, weights, w_down, addend=None, addend_gate=None):
+def expert_down(h, ids, weights, w_down, addend=None, addend_gate=None, identity=None):
     T, top = ids.shape
+    E = w_down.shape[0]
     out = torch.zeros((T, w_down.shape[1]), dtype=torch.float32, device=h.device)
     for t in range(T):
         for j in range(top):
             w = 1.0 if weights is None else weights[t, j]
-            out[t] += w * (w_down[int(ids[t, j])].to(torch.float32) @ h[t * top + j].to(torch.float32))
+            e = int(ids[t, j])
+            if e < E:
+                out[t] += w * (w_down[e].to(torch.float32) @ h[t * top + j].to(torch.float32))
+            elif identity is not None and e < E + identity[1]:
+                out[t] += w * identity[0][t].to(torch.float32)
     if addend is None:
         return out
     return out + (addend if addend_gate is None else addend * torch.sigmoid(addend_gate[:, :1]))
