@@ -212,7 +212,8 @@ def forward(cfg, w, tokens):
     T = len(tokens)
     positions = np.arange(T)
     x0 = w["embed"][np.asarray(tokens)] * float(cfg["embedding"]["scale"])
-    n_streams = int(cfg.get("streams") or 1)
+    copies = cfg.get("streams")                      # absent: one stream and the plain residual sum
+    n_streams = int(copies or 1)
     xs = [x0.copy() for _ in range(n_streams)]
     after, caches = [], {}
 
@@ -220,6 +221,9 @@ def forward(cfg, w, tokens):
         nonlocal xs
         p = f"l{i}."
         hc = f"{p}hc{which}."
+        if copies is None:
+            xs = [xs[0] + fn(layer_norm(xs[0], w[f"{p}norm{which}"], w[f"{p}norm{which}.b"], eps)) * w[f"{p}ls{which}"]]
+            return
         u = sum(w[hc + "in"][s] * xs[s] for s in range(n_streams))
         y = fn(layer_norm(u, w[f"{p}norm{which}"], w[f"{p}norm{which}.b"], eps)) * w[f"{p}ls{which}"]
         xs = [sum(w[hc + "mix"][s, t] * xs[s] for s in range(n_streams)) + w[hc + "out"][t] * y for t in range(n_streams)]
