@@ -8,6 +8,7 @@
     python bench.py --workload kubedra [--shape 1b]   # the Kubedra design beside a Llama of equal width and depth, and its kernels
     python bench.py --workload komulorn [--shape 1b]  # the Komulorn design beside a Llama of equal width, heads and depth, and its kernels
     python bench.py --workload zemezen [--shape 1b]   # the Zemezen design beside a Kubedra of equal width and depth, and its kernels
+    python bench.py --workload sopalorn [--shape 1b]  # the Sopalorn design beside a Zemezen of equal width and depth, and its kernels
     python bench.py --impl plain-cpu                  # the plain implementation under tests/, timed on the CPU
 
 A "step" is one decode step: one new token for each of ``batch`` sequences that already hold
@@ -129,14 +130,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--repeats", type=int, default=5, help="repetitions of every timed region (best and CV are reported)")
-    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts", "kubedra", "komulorn", "zemezen"],
+    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts", "kubedra", "komulorn", "zemezen", "sopalorn"],
                     help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps; "
                          "staggered: Model.generate on 64 prompts whose requests end five steps apart; "
                          "short-prompts: the time to the first token of single prompts of 20 to 1,024 tokens; "
                          "kubedra: prefill and decode of the Kubedra design at layer sizes of a real model beside a Llama of "
                          "equal width and depth, and each of its kernels against its roofline; "
                          "komulorn: the same for the Komulorn design beside a Llama of equal width, heads and depth; "
-                         "zemezen: the same for the Zemezen design beside a Kubedra of equal width and depth")
+                         "zemezen: the same for the Zemezen design beside a Kubedra of equal width and depth; "
+                         "sopalorn: the same for the Sopalorn design beside a Zemezen of equal width and depth")
     ap.add_argument("--no-generate", action="store_true", help="skip the Model.generate cells")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -172,6 +174,8 @@ def main():
         return komulorn_workload(args)
     if args.workload == "zemezen":
         return zemezen_workload(args)
+    if args.workload == "sopalorn":
+        return sopalorn_workload(args)
     pk = peaks()
     shape_name, shape = SHAPES[args.shape]
     cfg_dict = dict(shape, num_hidden_layers=args.layers or shape["num_hidden_layers"])
@@ -891,6 +895,177 @@ def zemezen_workload(args):
                       "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16",
                       "data": "synthetic", "vs_baseline": None, "clocks": sampler.stop(),
                       "config": {"model": "Zemezen, four layers at the sizes named", "batch": 8, "context": ctx, "prefill_tokens": T,
+                                 "l2": "flushed between a kernel's timed launches"},
+                      "peaks": pk, "sizes": out}))
+    return 0
+
+
+def sopalorn_workload(args):
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 at context 2,048) tokens per second of a four-layer
+    Sopalorn model at a real model's layer sizes (two copies of the stream), beside a four-layer Zemezen (the closest design
+    here: a delta rule, windowed attention with sinks, experts scored by a softmax over all) of the same width, heads,
+    state, window and feed-forward sizes; then every kernel the design added or changed, alone, against its roofline, beside
+    the like kernel of the closest path.  Random weights, synthetic tokens, bfloat16, CUDA events, an L2 flush between the
+    timed launches of a kernel."""
+    import numpy as np
+    import torch
+    from dotllm_b200 import Model
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.engine.step import AttentionPlan
+    from dotllm_b200.kernels import ops
+    tools = design_bench_tools(args)
+    pk, hbm, tflops, dev, T, ctx, sampler, timed, model_points = (tools.pk, tools.hbm, tools.tflops, tools.dev, tools.T, tools.ctx,
+                                                                  tools.sampler, tools.timed, tools.model_points)
+    sizes = ["1b", "8b"] if args.shape not in ("1b",) else ["1b"]
+    COPIES = 2
+
+    def kernel_table(z):
+        W, H, dk, dv, K, E, top = z["width"], z["heads"], z["key"], z["value"], z["conv"], z["experts"], z["top"]
+        nh, nkv, hd, window = z["att_heads"], z["att_kv"], z["att_dim"], z["window"]
+        bf = torch.bfloat16
+        rows = {}
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+
+        def row(name, fn, bytes_=0, flops=0):
+            us = timed(fn) * 1000.0
+            need = max(bytes_ / hbm, flops / tflops) * 1e6
+            rows[name] = {"us": round(us, 1), "roofline_us": round(need, 2), "frac": round(need / us, 4)}
+        for label, n, n_seqs in (("prefill", T, 1), ("decode", 64, 64)):
+            # the stream of copies: write, read and layer norm in one pass, beside the residual add fused into an RMS norm
+            x = torch.randn(n, COPIES * W, device=dev)
+            y = torch.randn(n, W, device=dev)
+            ones = torch.ones(W, device=dev)
+            write = ops.StreamWrite(y, ones, torch.eye(COPIES, device=dev), torch.ones(COPIES, device=dev))
+            read = torch.full((COPIES,), 1.0 / COPIES, device=dev)
+            row(f"stream_norm (write, read, layer norm; {COPIES} copies) {label}",
+                lambda: ops.stream_norm(x, COPIES, write, read, ones, ones, 1e-5, bf), bytes_=n * W * (8 * COPIES + 4 + 2))
+            xr = torch.randn(n, W, device=dev)
+            row(f"llama add_rmsnorm {label}", lambda: ops.add_rmsnorm(xr, y, ones, 1e-5, bf), bytes_=n * W * (8 + 4 + 2))
+            # the two recurrences: a constant decay per head beside a decay per key channel from logits; a decay per head in
+            # the delta rule beside one per key channel
+            kw, vw = H * dk, H * dv
+            C = 2 * kw + vw
+            proj = torch.randn(n, C + H, device=dev).to(bf)
+            cu = torch.arange(0, n + 1, n // n_seqs, dtype=torch.int32, device=dev)
+            seq = torch.arange(n, dtype=torch.int32, device=dev) // (n // n_seqs)
+            slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+            state = torch.zeros(n_seqs + 1, H, dk, dv, device=dev)
+            decay = torch.full((H,), 0.97, device=dev)
+            zz, zb = torch.randn(n, kw, device=dev), torch.zeros(kw, device=dev)
+            scan_io = 2 * n_seqs * H * dk * dv * 4 + n * vw * 4
+            row(f"gla_scan, constant decays, silu {label}",
+                lambda: ops.gla_scan(proj[:, :kw], proj[:, kw:2 * kw], proj[:, 2 * kw:2 * kw + vw], None, decay, cu, slots, state, H, dk, dv, 1.0),
+                bytes_=n * C * 2 + scan_io, flops=4 * n * H * dk * dv)
+            row(f"kubedra gla_scan {label}",
+                lambda: ops.gla_scan(proj[:, :kw], proj[:, kw:2 * kw], proj[:, 2 * kw:2 * kw + vw], zz, zb, cu, slots, state, H, dk, dv,
+                                     dk ** -0.5, 16.0), bytes_=n * (C * 2 + kw * 4) + scan_io, flops=4 * n * H * dk * dv)
+            taps = (torch.randn(C, K, device=dev) * 0.5).to(bf)
+            memory = torch.zeros(n_seqs + 1, H * dk * dv + (K - 1) * C, device=dev)
+            zh, zhb, a_log = torch.randn(n, H, device=dev), torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+            row(f"delta_rule, a decay per head {label}",
+                lambda: ops.delta_rule(proj, taps, proj[:, C:], zh, zhb, a_log, seq, cu, slots, memory, H, H, dk, dv, dk ** -0.5, 1e-6,
+                                       head_decay=True), bytes_=n * (C * 2 + H * 4) + scan_io, flops=6 * n * H * dk * dv)
+            row(f"zemezen delta_rule, a decay per key channel {label}",
+                lambda: ops.delta_rule(proj, taps, proj[:, C:], zz, zb, a_log, seq, cu, slots, memory, H, H, dk, dv, dk ** -0.5, 1e-6),
+                bytes_=n * (C * 2 + kw * 4) + scan_io, flops=6 * n * H * dk * dv)
+            o = torch.randn(n, vw, device=dev)
+            g = torch.randn(n, vw, device=dev).to(bf)
+            row(f"head_norm_gate over all heads at once, sigmoid {label}",
+                lambda: ops.head_norm_gate(o, g, torch.ones(vw, device=dev), 1, vw, 1e-5, bf, gate="sigmoid"), bytes_=n * vw * (4 + 2 + 2))
+            row(f"zemezen head_norm_gate per head, sigmoid {label}",
+                lambda: ops.head_norm_gate(o, g, torch.ones(dv, device=dev), H, dv, 1e-5, bf, gate="sigmoid"), bytes_=n * vw * (4 + 2 + 2))
+            # queries and keys normalised over their whole projections beside the norm per head
+            qk = torch.randn(n, (nh + 2 * nkv) * hd, device=dev).to(bf)
+            row(f"group_rmsnorm (whole query and key projections) {label}",
+                lambda: ops.group_rmsnorm(qk[:, :(nh + nkv) * hd], torch.ones((nh + nkv) * hd, device=dev), nh * hd, nkv * hd, 1e-5),
+                bytes_=n * (nh + nkv) * hd * 4)
+            gq = torch.ones(hd, device=dev)
+            row(f"zemezen head_rmsnorm (queries and keys) {label}", lambda: ops.head_rmsnorm(qk[:, :(nh + nkv) * hd], gq, nh, hd, 1e-5, gq, nkv),
+                bytes_=n * (nh + nkv) * hd * 4)
+            # the two sides of a parallel layer normalised and averaged, beside a branch normalised and added
+            a, b = torch.randn(n, W, device=dev), torch.randn(n, W, device=dev)
+            row(f"pair_norm_sum {label}", lambda: ops.pair_norm_sum(a, b, ones, ones, 1e-5), bytes_=n * W * 12)
+            row(f"kubedra branch_norm_add {label}", lambda: ops.add_normed_branch(xr, ops.NormedBranch(a, ones, 1e-5)), bytes_=n * W * 12)
+            # attention over every earlier key with one added to the denominator beside plain attention; the window with
+            # learned sinks is the Zemezen path's kernel as it is
+            per = ctx if label == "decode" else n
+            pages = (per + 63) // 64
+            k_pool = torch.randn(n_seqs * pages + 1, nkv, 64, hd, device=dev).to(bf)
+            v_pool = torch.randn(n_seqs * pages + 1, nkv, hd, 64, device=dev).to(bf)
+            table = torch.arange(n_seqs * pages, dtype=torch.int32, device=dev).reshape(n_seqs, pages)
+            starts, news = ([0], [n]) if label == "prefill" else ([ctx - 1] * n_seqs, [1] * n_seqs)
+            totals = [s0 + s1 for s0, s1 in zip(starts, news)]
+            pos = i32([s0 + i for s0, s1 in zip(starts, news) for i in range(s1)])
+            q = qk[:, :nh * hd]
+            sinks = torch.zeros(nh, device=dev)
+            seen = sum(p + 1 for p in pos.tolist())
+            att_bytes = per * n_seqs * nkv * hd * 2 * 2 + n * nh * hd * 4
+            for name, kw_ in (("attention, one added to the denominator", dict(sinks=sinks)), ("llama attention", {})):
+                plan = AttentionPlan(n_seqs, max(news), max(totals), label == "decode", i32(starts), i32(news),
+                                     i32([0] + list(np.cumsum(news))), i32(totals), list(starts), list(news))
+                row(f"{name} {label}", lambda: ops.attention(q, k_pool, v_pool, seq, pos, table, nh, nkv, hd, hd ** -0.5, 0, plan=plan, **kw_),
+                    bytes_=att_bytes, flops=4 * seen * nh * hd)
+            del k_pool, v_pool
+            # the router: corrected shares, normalised and scaled weights, beside the softmax over all with groups
+            xb = torch.randn(n, W, device=dev).to(bf)
+            n_id = z["identity"]
+            wr = torch.randn((E + n_id + 7) // 8 * 8, W, device=dev).to(bf)
+            corr = torch.randn(E + n_id, device=dev) * 0.01
+            row(f"route_topk, corrected shares, normalised {label}",
+                lambda: ops.route_topk(xb, wr, None, top, scoring="softmax_all", experts=E + n_id, correction=corr, normalise=True, weight_scale=2.0),
+                bytes_=n * W * 2 + (E + n_id) * W * 2, flops=2 * n * (E + n_id) * W)
+            row(f"zemezen route_topk, groups {label}", lambda: ops.route_topk(xb, wr[:E], None, top, scoring="softmax_all", groups=z["groups"]),
+                bytes_=n * W * 2 + E * W * 2, flops=2 * n * E * W)
+        return rows
+
+    out = {}
+    for name in sizes:
+        z = dict(ZEMEZEN_SIZES[name], identity=4)
+        vocab = 32000
+        smoe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+                "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.0}}
+        sdense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+        rot = {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+        att = {"heads": z["att_heads"], "kv_heads": z["att_kv"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5, "rot": rot}
+        left = {"heads": z["att_heads"], "kv_heads": z["att_kv"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5,
+                "mask": {"size": z["window"]}}
+        right = {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["key"], "vdim": z["value"], "conv": z["conv"]}
+        light = {"heads": z["heads"], "dim": z["key"], "vdim": z["value"], "decay": [1.0 - 2.0 ** -(2 + i % 8) for i in range(z["heads"])]}
+        scfg = {"architecture": "Sopalorn", "vocab": vocab, "width": z["width"], "max_positions": 8192, "norm": {"eps": 1e-5},
+                "embedding": {"scale": 1.0}, "logit_scale": 1.0, "streams": COPIES,
+                "layers": [{"type": "lightning", "mixer": light, "mlp": sdense},
+                           {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": smoe},
+                           {"type": "attention", "mixer": att, "mlp": sdense},
+                           {"type": "attention", "mixer": dict(att, kv_from=2), "mlp": smoe}]}
+        moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+               "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+        dense = {"kind": "dense", "ff": z["ff"]}
+        mix_d = {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["key"], "vdim": z["value"], "conv": z["conv"], "ranks": [64, 64]}
+        mix_a = {"heads": z["att_heads"], "kv_heads": z["att_kv"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5,
+                 "mask": {"size": z["window"], "keep_first": z["keep"]}, "rot": {"dims": z["rot"], "base": 10000.0}}
+        mix_full = dict(mix_a)
+        del mix_full["mask"]
+        # the closest model here, layer by layer: a recurrence + dense, a delta rule + experts (the parallel layer's windowed
+        # attention is the fourth layer's kernel), attention over every key + dense, windowed attention + experts
+        zcfg = {"architecture": "Zemezen", "vocab": vocab, "width": z["width"], "max_positions": 8192, "norm": {"eps": 1e-5},
+                "layers": [{"type": "channel_delta", "mixer": mix_d, "mlp": dense}, {"type": "channel_delta", "mixer": mix_d, "mlp": moe},
+                           {"type": "attention", "mixer": mix_full, "mlp": dense}, {"type": "attention", "mixer": mix_a, "mlp": moe}]}
+        point = {}
+        for label, cfg_dict in (("sopalorn", scfg), ("zemezen", zcfg)):
+            model = Model.random(config_from_dict(cfg_dict), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+            point[label] = model_points(model, vocab)
+            print(f"[bench] {name} {label}: {point[label]}", file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        point["kernels"] = kernel_table(z)
+        for k, v in point["kernels"].items():
+            print(f"[bench] {name} {k}: {v}", file=sys.stderr, flush=True)
+        out[name] = point
+    first = out[sizes[0]]
+    print(json.dumps({"metric": "sopalorn_decode_tokens_per_second", "value": first["sopalorn"]["decode_b8_tok_s"], "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16",
+                      "data": "synthetic", "vs_baseline": None, "clocks": sampler.stop(),
+                      "config": {"model": "Sopalorn, four layers at the sizes named", "batch": 8, "context": ctx, "prefill_tokens": T,
                                  "l2": "flushed between a kernel's timed launches"},
                       "peaks": pk, "sizes": out}))
     return 0

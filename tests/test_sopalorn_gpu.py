@@ -417,7 +417,8 @@ def test_far_keys_rotation_and_the_added_one_decide_whole_rows(tmp):
         without = ts.plain_logits(soft_cfg, soft_w, tokens[:150])
     finally:
         ps.softmax_attention = saved[0]
-    assert int(((without - soft_ref).pow(2).mean(-1).sqrt() / soft_ref.pow(2).mean(-1).sqrt() > 1e-2).sum()) >= 20
+    # (where the keys are few: the first tokens of a sequence, whose sum of weights is of the order of the one)
+    assert int(((without - soft_ref).pow(2).mean(-1).sqrt() / soft_ref.pow(2).mean(-1).sqrt() > 1e-2)[:12].sum()) >= 6
     for cuts in ([150], [70, 2], [3]):
         assert rel_err(run_cuts(soft_model, tokens[:150], cuts), soft_ref) < 1e-4, cuts
     bf = load_pair(tmp, "sharp_far", torch.bfloat16, change=_sharpen_far, tag="far")
