@@ -201,8 +201,6 @@ class SopalornLayerConfig:
         if not isinstance(d.get("mixer"), dict):
             raise ConfigError(f"config.json: {where} lacks its mixer's sizes")
         mixer = _MIXERS[kind].from_dict(d["mixer"], where + ".mixer")
-        if kind == "attention" and mixer.window is not None:
-            raise ConfigError(f"config.json: {where}.mixer: an attention layer of this design sees every earlier key")
         mlp = FeedForwardConfig.from_dict(d["mlp"], where + ".mlp") if d.get("mlp") else None
         return cls(kind, mixer, mlp)
 
@@ -238,8 +236,8 @@ class SopalornConfig:
             if not 0 <= j < i or parsed[j].type != "attention" or parsed[j].mixer.kv_from is not None:
                 raise ConfigError(f"config.json: layers[{i}].mixer.kv_from = {j} must name an earlier attention layer with keys of its own")
             a, b = layer.mixer, parsed[j].mixer
-            if (a.kv_heads, a.dim, a.vdim, a.rot) != (b.kv_heads, b.dim, b.vdim, b.rot):
-                raise ConfigError(f"config.json: layers[{i}] reads the keys and values of layer {j}, whose heads, widths or rotation differ")
+            if (a.kv_heads, a.dim, a.vdim, a.rot, a.window) != (b.kv_heads, b.dim, b.vdim, b.rot, b.window):
+                raise ConfigError(f"config.json: layers[{i}] reads the keys and values of layer {j}, whose heads, widths, rotation or window differ")
         eos = d.get("eos_token_id")
         eos = () if eos is None else tuple(int(t) for t in (eos if isinstance(eos, (list, tuple)) else [eos]))
         cfg = cls(_get(d, "vocab", int, "config"), _get(d, "width", int, "config"), _get(d.get("norm"), "eps", float, "norm"), parsed,

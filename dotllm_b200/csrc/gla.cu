@@ -237,6 +237,44 @@ head_norm_gate_kernel(const float* __restrict__ o, int o_stride, const T* __rest
     }
 }
 
+// The same for heads wider than a warp walks well (a norm over all heads' outputs at once is one head as wide as all): a
+// block per (token, head), the row's values waiting in registers across the reduction.
+#define HNG_WIDE_THREADS 256
+#define HNG_WIDE_MIN 1024
+#define HNG_WIDE_PER_THREAD 32           // values a thread keeps: rows of up to 8192 values
+template <typename T>
+__global__ void __launch_bounds__(HNG_WIDE_THREADS)
+head_norm_gate_wide_kernel(const float* __restrict__ o, int o_stride, const T* __restrict__ g, int g_stride,
+                           const float* __restrict__ gain, T* __restrict__ out, int out_stride, int H, int vdim, float eps,
+                           int gate_kind) {
+    __shared__ float scratch[33];
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int t = blockIdx.x / H, h = blockIdx.x % H;
+    const float* orow = o + (size_t)t * o_stride + (size_t)h * vdim;
+    const T* grow = g + (size_t)t * g_stride + (size_t)h * vdim;
+    float v[HNG_WIDE_PER_THREAD], gt[HNG_WIDE_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < HNG_WIDE_PER_THREAD; ++i) {
+        const int j = threadIdx.x + i * HNG_WIDE_THREADS;
+        v[i] = j < vdim ? orow[j] : 0.f;
+        gt[i] = j < vdim ? dl_to_f32<T>(grow[j]) : 0.f;
+        ss += v[i] * v[i];
+    }
+    ss = dl_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)vdim + eps);
+    T* dst = out + (size_t)t * out_stride + (size_t)h * vdim;
+#pragma unroll
+    for (int i = 0; i < HNG_WIDE_PER_THREAD; ++i) {
+        const int j = threadIdx.x + i * HNG_WIDE_THREADS;
+        if (j < vdim) {
+            const float sig = 1.0f / (1.0f + expf(-gt[i]));
+            dst[j] = dl_from_f32<T>(v[i] * scale * gain[j] * (gate_kind == 1 ? sig : gt[i] * sig));
+        }
+    }
+}
+
 extern "C" int dl_head_norm_gate(const float* o, int o_stride, const void* g, int g_stride, const float* gain, void* out,
                                  int out_stride, int dtype, int rows, int H, int vdim, float eps, int gate_kind, void* stream) {
     DL_REQUIRE(rows >= 0 && H > 0 && vdim > 0 && eps > 0.f, "head_norm_gate: bad arguments");
@@ -246,6 +284,17 @@ extern "C" int dl_head_norm_gate(const float* o, int o_stride, const void* g, in
     const long warps = (long)rows * H;
     const dim3 grid((unsigned)((warps + 3) / 4)), block(128);
     cudaError_t e;
+    if (vdim >= HNG_WIDE_MIN && vdim <= HNG_WIDE_THREADS * HNG_WIDE_PER_THREAD && (dtype == DL_F32 || dtype == DL_BF16)) {
+        const dim3 wide((unsigned)warps), threads(HNG_WIDE_THREADS);
+        if (dtype == DL_F32)
+            e = dl_launch_dependent(head_norm_gate_wide_kernel<float>, wide, threads, 0, s, o, o_stride, (const float*)g, g_stride, gain,
+                                    (float*)out, out_stride, H, vdim, eps, gate_kind);
+        else
+            e = dl_launch_dependent(head_norm_gate_wide_kernel<__nv_bfloat16>, wide, threads, 0, s, o, o_stride, (const __nv_bfloat16*)g,
+                                    g_stride, gain, (__nv_bfloat16*)out, out_stride, H, vdim, eps, gate_kind);
+        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "head_norm_gate: %s", cudaGetErrorString(e));
+        return DL_OK;
+    }
     if (dtype == DL_F32)
         e = dl_launch_dependent(head_norm_gate_kernel<float>, grid, block, 0, s, o, o_stride, (const float*)g, g_stride, gain,
                                 (float*)out, out_stride, rows, H, vdim, eps, gate_kind);

@@ -22,7 +22,7 @@
 #include "common.cuh"
 
 #define ST_THREADS 256
-#define ST_MAX_COPIES 8
+#define ST_MAX_COPIES 16
 
 template <typename TY, typename TOut>
 __global__ void __launch_bounds__(ST_THREADS)
@@ -93,6 +93,116 @@ stream_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, int y_stride
     }
 }
 
+// The same pass for rows of up to 4 * ST_THREADS * ST_MAX_VEC values whose width is a multiple of 4, and up to four copies:
+// every thread loads its 16-byte pieces of all copies and of y at once (a decode step has a handful of rows, so the
+// kernel's time is one round of memory latency, not a loop of them) and keeps its pieces of u in registers across the two
+// reductions.  The arithmetic per value and its order are the looped kernel's; the block sums add the same partial sums in
+// another order.
+#define ST_MAX_VEC 8
+
+template <typename T> struct StVec4;
+template <> struct StVec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct StVec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+__device__ __forceinline__ float4 st_fma4(float a, float4 x, float4 acc) {
+    return make_float4(fmaf(a, x.x, acc.x), fmaf(a, x.y, acc.y), fmaf(a, x.z, acc.z), fmaf(a, x.w, acc.w));
+}
+
+template <typename TY, typename TOut, int S, int NV>
+__global__ void __launch_bounds__(ST_THREADS)
+stream_norm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, int y_stride, const float* __restrict__ scale,
+                       const float* __restrict__ mix, const float* __restrict__ outw, const float* __restrict__ read,
+                       const float* __restrict__ gain, const float* __restrict__ bias, TOut* __restrict__ normed,
+                       float* __restrict__ summed, int width, float eps, int kind) {
+    __shared__ float scratch[33];
+    dl_launch_dependents();
+    float w_mix[S * S], w_out[S], w_read[S];
+#pragma unroll
+    for (int i = 0; i < S * S; ++i) w_mix[i] = mix != nullptr ? mix[i] : 0.f;
+#pragma unroll
+    for (int i = 0; i < S; ++i) { w_out[i] = outw != nullptr ? outw[i] : 0.f; w_read[i] = read != nullptr ? read[i] : 1.f; }
+    dl_grid_dependency_wait();
+    float* row = x + (size_t)blockIdx.x * S * width;
+    const int n_vec = width / 4;
+    const bool write = y != nullptr;
+    float4 u[NV];
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * ST_THREADS;
+        u[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c >= n_vec) continue;
+        float4 old[S];
+#pragma unroll
+        for (int s = 0; s < S; ++s) old[s] = StVec4<float>::load(row + (size_t)s * width + 4 * c);
+        if (write) {
+            float4 yy = StVec4<TY>::load(y + (size_t)blockIdx.x * y_stride + 4 * c);
+            if (scale != nullptr) {
+                const float4 sc = StVec4<float>::load(scale + 4 * c);
+                yy = make_float4(yy.x * sc.x, yy.y * sc.y, yy.z * sc.z, yy.w * sc.w);
+            }
+#pragma unroll
+            for (int t = 0; t < S; ++t) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < S; ++s) acc = st_fma4(w_mix[s * S + t], old[s], acc);
+                acc = st_fma4(w_out[t], yy, acc);
+                StVec4<float>::store(row + (size_t)t * width + 4 * c, acc);
+                u[i] = st_fma4(w_read[t], acc, u[i]);
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < S; ++t) u[i] = st_fma4(w_read[t], old[t], u[i]);
+        }
+        if (summed != nullptr) StVec4<float>::store(summed + (size_t)blockIdx.x * width + 4 * c, u[i]);
+        total += kind == 0 ? (u[i].x + u[i].y) + (u[i].z + u[i].w) : (u[i].x * u[i].x + u[i].y * u[i].y) + (u[i].z * u[i].z + u[i].w * u[i].w);
+    }
+    if (normed == nullptr) return;
+    total = dl_block_sum(total, scratch);
+    float mean = 0.f, factor;
+    if (kind == 0) {
+        mean = total / (float)width;
+        float dev = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (threadIdx.x + i * ST_THREADS >= n_vec) continue;
+            const float a = u[i].x - mean, b = u[i].y - mean, c2 = u[i].z - mean, d = u[i].w - mean;
+            dev += (a * a + b * b) + (c2 * c2 + d * d);
+        }
+        dev = dl_block_sum(dev, scratch);
+        factor = 1.0f / sqrtf(dev / (float)width + eps);
+    } else {
+        factor = 1.0f / sqrtf(total / (float)width + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * ST_THREADS;
+        if (c >= n_vec) continue;
+        const float4 gn = StVec4<float>::load(gain + 4 * c);
+        const float4 bs = bias != nullptr ? StVec4<float>::load(bias + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        StVec4<TOut>::store(normed + (size_t)blockIdx.x * width + 4 * c,
+                            make_float4((u[i].x - mean) * factor * gn.x + bs.x, (u[i].y - mean) * factor * gn.y + bs.y,
+                                        (u[i].z - mean) * factor * gn.z + bs.z, (u[i].w - mean) * factor * gn.w + bs.w));
+    }
+}
+
 // x float32 [rows, S * width], updated in place when y is given; y [rows, width] of y_dtype (rows y_stride apart) or NULL
 // (nothing is written); scale float32 [width] or NULL; mix float32 [S, S] (from, to), outw float32 [S] (both needed with
 // y); read float32 [S] or NULL (every copy counts once); gain float32 [width], bias float32 [width] or NULL; normed
@@ -121,6 +231,36 @@ extern "C" int dl_stream_norm(float* x, const void* y, int y_dtype, int y_stride
     } while (0)
     const bool y16 = y != nullptr && y_dtype == DL_BF16;
     DL_REQUIRE(y == nullptr || y_dtype == DL_F32 || y_dtype == DL_BF16, "stream_norm: y dtype %d", y_dtype);
+    DL_REQUIRE(normed == nullptr || out_dtype == DL_F32 || out_dtype == DL_BF16, "stream_norm: out dtype %d", out_dtype);
+    const auto aligned = [](const void* p) { return ((uintptr_t)p % 16) == 0; };
+    const bool vec = S <= 4 && width % 4 == 0 && width <= 4 * ST_THREADS * ST_MAX_VEC && aligned(x) && aligned(scale) && aligned(gain) &&
+                     aligned(bias) && aligned(normed) && aligned(summed) && (y == nullptr || (aligned(y) && y_stride % 4 == 0));
+    if (vec) {
+        const int nv = (width / 4 + ST_THREADS - 1) / ST_THREADS;           // 16-byte pieces a thread
+#define ST_VEC3(TY, TOUT, SS, NV)                                                                                            \
+        e = dl_launch_dependent(stream_norm_vec_kernel<TY, TOUT, SS, NV>, grid, block, 0, s, x, (const TY*)y, y_stride, scale, mix,   \
+                                outw, read, gain, bias, (TOUT*)normed, summed, width, eps, kind)
+#define ST_VEC2(TY, TOUT, SS)                                                                                                \
+        do {                                                                                                                 \
+            if (nv <= 1) ST_VEC3(TY, TOUT, SS, 1); else if (nv <= 2) ST_VEC3(TY, TOUT, SS, 2);                               \
+            else if (nv <= 4) ST_VEC3(TY, TOUT, SS, 4); else ST_VEC3(TY, TOUT, SS, ST_MAX_VEC);                             \
+        } while (0)
+#define ST_VEC1(TY, TOUT)                                                                                                    \
+        do {                                                                                                                 \
+            if (S == 1) ST_VEC2(TY, TOUT, 1); else if (S == 2) ST_VEC2(TY, TOUT, 2);                                         \
+            else if (S == 3) ST_VEC2(TY, TOUT, 3); else ST_VEC2(TY, TOUT, 4);                                                \
+        } while (0)
+        const bool out16 = normed != nullptr && out_dtype == DL_BF16;
+        if (y16 && out16) ST_VEC1(__nv_bfloat16, __nv_bfloat16);
+        else if (y16) ST_VEC1(__nv_bfloat16, float);
+        else if (out16) ST_VEC1(float, __nv_bfloat16);
+        else ST_VEC1(float, float);
+#undef ST_VEC1
+#undef ST_VEC2
+#undef ST_VEC3
+        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "stream_norm: %s", cudaGetErrorString(e));
+        return DL_OK;
+    }
     if (normed == nullptr || out_dtype == DL_F32) {
         if (y16) ST_LAUNCH(__nv_bfloat16, float); else ST_LAUNCH(float, float);
     } else if (out_dtype == DL_BF16) {

@@ -27,7 +27,7 @@ class StreamConnection(Connection):
     a gain per channel on the sublayer's output); optional ``tensors``: local names of ``in``, ``out``, ``mix``, ``scale``."""
 
     NAMES = {"in": "in", "out": "out", "mix": "mix", "scale": "scale"}
-    MAX_COPIES = 8                # ST_MAX_COPIES in csrc/streams.cu
+    MAX_COPIES = 16               # ST_MAX_COPIES in csrc/streams.cu
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)

@@ -135,6 +135,12 @@ def test_norms_over_groups_of_columns_and_pairs_of_branches_alone(dtype):
               torch.float32)
     v = g32(3, 77, seed=9)
     assert torch.equal(ops.scale_values(v.clone(), 0.3).cpu(), v.cpu() * 0.3)
+    # a norm over all heads' outputs at once is one head as wide as all: widths on both sides of the kernel's wide form
+    for H, vdim in ((1, 1024), (1, 4096), (1, 1000), (1, 520), (2, 2048), (1, 8192)):
+        o, g, gain = g32(6, H * vdim, seed=5, scale=3.0), g32(6, H * vdim + 8, seed=6).to(dtype)[:, :H * vdim], g32(vdim, seed=7)
+        for gate in ("sigmoid", "silu"):
+            close(ops.head_norm_gate(o, g, gain, H, vdim, 1e-6, dtype, gate=gate),
+                  kernel_refs.head_norm_gate(o.cpu(), g.cpu(), gain.cpu(), H, vdim, 1e-6, dtype, gate=gate), dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
