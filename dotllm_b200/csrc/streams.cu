@@ -285,6 +285,40 @@ stream_copies_kernel(const float* __restrict__ src, float* __restrict__ dst, int
     }
 }
 
+// dst[r, s, :] = table[ids[r], :] * factor for every copy s, float32: the embedding straight into a stream of S copies.  An id
+// outside the table gives a row of zeros.
+template <typename T>
+__global__ void __launch_bounds__(ST_THREADS)
+embed_copies_kernel(const T* __restrict__ table, int table_stride, const int32_t* __restrict__ ids, float* __restrict__ dst, int S,
+                    int width, int n_table_rows, float factor) {
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int id = ids[blockIdx.x];
+    const bool ok = id >= 0 && id < n_table_rows;
+    const T* src = table + (size_t)(ok ? id : 0) * table_stride;
+    for (int c = threadIdx.x; c < width; c += ST_THREADS) {
+        const float v = ok ? dl_to_f32<T>(src[c]) * factor : 0.f;
+        for (int s = 0; s < S; ++s) dst[((size_t)blockIdx.x * S + s) * width + c] = v;
+    }
+}
+
+extern "C" int dl_embed_copies(const void* table, int dtype, int table_stride, const int32_t* ids, float* dst, int rows, int S,
+                               int width, int n_table_rows, float factor, void* stream) {
+    DL_REQUIRE(rows >= 0 && S > 0 && width > 0 && n_table_rows > 0 && table_stride >= width, "embed_copies: bad sizes");
+    if (rows == 0) return DL_OK;
+    cudaError_t e;
+    if (dtype == DL_F32)
+        e = dl_launch_dependent(embed_copies_kernel<float>, dim3(rows), dim3(ST_THREADS), 0, (cudaStream_t)stream, (const float*)table,
+                                table_stride, ids, dst, S, width, n_table_rows, factor);
+    else if (dtype == DL_BF16)
+        e = dl_launch_dependent(embed_copies_kernel<__nv_bfloat16>, dim3(rows), dim3(ST_THREADS), 0, (cudaStream_t)stream,
+                                (const __nv_bfloat16*)table, table_stride, ids, dst, S, width, n_table_rows, factor);
+    else
+        return dl_fail(DL_ERR_UNSUPPORTED, "embed_copies: dtype %d", dtype);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "embed_copies: %s", cudaGetErrorString(e));
+    return DL_OK;
+}
+
 extern "C" int dl_stream_copies(const float* src, float* dst, int rows, int S, int width, float factor, void* stream) {
     DL_REQUIRE(rows >= 0 && S > 0 && width > 0, "stream_copies: bad sizes");
     if (rows == 0) return DL_OK;

@@ -34,6 +34,7 @@ _library.register_signatures({
     "dl_expert_combine": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P],
     "dl_stream_norm": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _P],
     "dl_stream_copies": [_P, _P, _I, _I, _I, _F, _P],
+    "dl_embed_copies": [_P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
     "dl_group_rmsnorm": [_P, _I, _P, _I, _I, _P, _I, _I, _I, _F, _P],
     "dl_pair_norm_sum": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _F, _P],
     "dl_scale_values": [_P, ctypes.c_longlong, _F, _P],
@@ -331,6 +332,19 @@ def stream_copies(x, copies, factor=1.0):
         raise KernelError("stream_copies: need contiguous float32 [T, H]")
     out = torch.empty((x.shape[0], int(copies) * x.shape[1]), dtype=torch.float32, device=x.device)
     _library.call("dl_stream_copies", _ptr(x), _ptr(out), x.shape[0], int(copies), x.shape[1], float(factor), _stream())
+    return out
+
+
+def embed_copies(table, ids, copies, factor=1.0):
+    """out[r, s] = table[ids[r]] * factor for each of ``copies`` copies s: float32 [R, copies * width], the embedding as the
+    start of a stream of copies.  table [n, width] float32 or bfloat16 (rows contiguous); ids int32 [R]."""
+    _need_cuda(table, ids)
+    stride = _rows_view(table, "embed_copies table")
+    _int32(ids, "embed_copies ids")
+    n, width = table.shape
+    out = torch.empty((ids.numel(), int(copies) * width), dtype=torch.float32, device=table.device)
+    _library.call("dl_embed_copies", _ptr(table), _code(table.dtype), stride, _ptr(ids), _ptr(out), ids.numel(), int(copies), width, n,
+                  float(factor), _stream())
     return out
 
 

@@ -37,10 +37,9 @@ class TokenEmbedding(Part):
         """The step's tokens (``step.tokens`` int32 [T]) -> float32 [T, H]: the start of the residual
         stream.  An embedding gets the whole StepContext: one that also encodes positions reads
         ``step.token_pos``."""
-        rows = ops.gather_rows(self.table, step.tokens)
         if self.copies == 1 and self.scale == 1.0:
-            return rows
-        return ops.stream_copies(rows, self.copies, self.scale)
+            return ops.gather_rows(self.table, step.tokens)
+        return ops.embed_copies(self.table, step.tokens, self.copies, self.scale)
 
 
 class TokenPositionEmbedding(Part):

@@ -31,7 +31,7 @@ def cpu_kernels(monkeypatch):
                  "sample", "repetition_penalty", "add_normed_branch", "add_rows", "embed_positions", "gated_activation",
                  "gla_scan", "head_norm_gate", "route_topk", "expert_gate_up", "expert_down", "linear_per_head",
                  "unary_activation", "activated_linear", "softcap", "head_gate", "head_rmsnorm", "delta_rule", "stream_norm",
-                 "stream_copies", "group_rmsnorm", "pair_norm_sum", "scale_values", "StreamWrite"):
+                 "stream_copies", "embed_copies", "group_rmsnorm", "pair_norm_sum", "scale_values", "StreamWrite"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     monkeypatch.setattr(ops, "experts_grouped_takes", lambda *a, **k: False)     # the tensor-core path is the GPU's
     # ops.rope_cache_attention composes the two patched functions above for anything but CUDA bfloat16

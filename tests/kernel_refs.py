@@ -169,6 +169,10 @@ def stream_copies(x, copies, factor=1.0):
     return (x * factor).repeat(1, int(copies))
 
 
+def embed_copies(table, ids, copies, factor=1.0):
+    return (table[ids.long()].to(torch.float32) * factor).repeat(1, int(copies))
+
+
 def group_rmsnorm(x, gain, width_a, width_b, eps):
     xf = x.to(torch.float32)
     parts = [_rms(xf[:, :width_a], eps)] + ([_rms(xf[:, width_a:width_a + width_b], eps)] if width_b else [])

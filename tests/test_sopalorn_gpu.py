@@ -120,6 +120,8 @@ def test_stream_of_copies_write_read_and_norm_alone(S, H, kind, dtype):
             close(xa, xb, torch.float32)
     copies = ops.stream_copies(x[:, :H].contiguous(), S, 0.7)
     assert torch.equal(copies.cpu(), kernel_refs.stream_copies(x[:, :H].cpu(), S, 0.7))
+    table, ids = g32(11, H + 4, seed=9).to(dtype)[:, :H], torch.tensor([3, 0, 10, 3], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embed_copies(table, ids, S, 0.7).cpu(), kernel_refs.embed_copies(table.cpu(), ids.cpu(), S, 0.7))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
