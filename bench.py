@@ -1025,7 +1025,7 @@ def sopalorn_workload(args):
         smoe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
                 "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.0}}
         sdense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
-        rot = {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+        rot = {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
         att = {"heads": z["att_heads"], "kv_heads": z["att_kv"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5, "rot": rot}
         left = {"heads": z["att_heads"], "kv_heads": z["att_kv"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5,
                 "mask": {"size": z["window"]}}

@@ -112,10 +112,10 @@ SHARP_WINDOW = config(64, 120, 1e-5, 2, [parallel((4, 2, 16, 16, 6.0, 23), (2, 1
 SHARP_FAR = config(64, 120, 1e-5, 2, [attention(4, 2, 16, 16, 6.0, rotation(8, 100.0, (4.0, 64, 8.0, 1.0)))])
 # Layers at the widths of a real model's layers: heads of 128 channels, experts of 512.
 WIDE = config(1024, 1000, 1e-5, 2,
-              [attention(8, 2, 128, 128, 128 ** -0.5, rotation(64, 10000.0, (8.0, 1024, 32.0, 1.0)), mlp=moe(8, 2, 2, 512, 2.0)),
+              [attention(8, 2, 128, 128, 128 ** -0.5, rotation(64, 10000.0, (16.0, 512, 24.0, 0.5)), mlp=moe(8, 2, 2, 512, 2.0)),
                parallel((8, 2, 128, 128, 128 ** -0.5, 100), (8, 4, 128, 128, 4), mlp=dense(2048, 7.0)),
                lightning(8, 128, 128, tuple(1.0 - 2.0 ** -(i + 2) for i in range(8)), mlp=dense(1024, 7.0)),
-               attention(8, 2, 128, 128, 128 ** -0.5, rotation(64, 10000.0, (8.0, 1024, 32.0, 1.0)), kv_from=0, mlp=None)],
+               attention(8, 2, 128, 128, 128 ** -0.5, rotation(64, 10000.0, (16.0, 512, 24.0, 0.5)), kv_from=0, mlp=None)],
               embedding_scale=1.0, logit_scale=0.25)
 CONFIGS.update(wide=WIDE, sharp_window=SHARP_WINDOW, sharp_far=SHARP_FAR)
 
@@ -148,7 +148,7 @@ def random_config(rng):
             kv = rng.choice([1, 1, 2, 3, 4])
             dim = rng.choice([8, 16, 24, 32, 40, 48, 64, 64, 80, 96, 128])
             rd = rng.choice([0, dim, dim // 2 - (dim // 2) % 2, 2 * rng.randrange(1, dim // 2 + 1)])
-            scaling = rng.choice([None, (8.0, 1024, 32.0, 1.0), (4.0, 64, 8.0, 0.5), (40.0, 4096, 16.0, 2.0)])
+            scaling = rng.choice([None, (8.0, 2048, 24.0, 1.0), (4.0, 64, 8.0, 0.5), (40.0, 4096, 16.0, 2.0)])
             layers.append(attention(kv * rng.choice([1, 2, 3, 4, 6]), kv, dim, rng.choice([dim, dim, 8, 20, 64]),
                                     rng.choice([0.1, 0.2, 0.35, dim ** -0.5]),
                                     rotation(rd, rng.choice([100.0, 10000.0, 500000.0]), scaling) if rd else None, mlp=mlp))
