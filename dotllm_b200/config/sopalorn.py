@@ -156,7 +156,7 @@ _MIXERS = {"attention": AttentionConfig, "lightning": LightningConfig, "parallel
 class FeedForwardConfig:
     kind: str                             # "dense" or "moe"
     ff: int                               # dense: the hidden width; moe: one expert's
-    limit: float = 0.0                    # dense: the clamp of gate and up
+    limit: float = 0.0                    # dense: the clamp of gate and up (0, or no key: none)
     experts: int = 0                      # experts with matrices
     identity: int = 0                     # experts without: they give back their input
     top: int = 0
@@ -166,9 +166,9 @@ class FeedForwardConfig:
     def from_dict(cls, d, where):
         kind = _get(d, "kind", str, where)
         if kind == "dense":
-            cfg = cls("dense", _get(d, "ff", int, where), _get(d, "limit", float, where))
-            if cfg.ff <= 0 or cfg.limit <= 0:
-                raise ConfigError(f"config.json: {where}: ff and limit must be positive")
+            cfg = cls("dense", _get(d, "ff", int, where), _get(d, "limit", float, where, default=0.0, required=False))
+            if cfg.ff <= 0 or cfg.limit < 0:
+                raise ConfigError(f"config.json: {where}: ff must be positive and limit not negative")
             return cfg
         if kind != "moe":
             raise ConfigError(f"config.json: {where}.kind = {kind!r}; known: 'dense', 'moe'")
@@ -182,7 +182,7 @@ class FeedForwardConfig:
 
     def to_dict(self):
         if self.kind == "dense":
-            return {"kind": "dense", "ff": self.ff, "limit": self.limit}
+            return {"kind": "dense", "ff": self.ff, **({"limit": self.limit} if self.limit else {})}
         return {"kind": "moe", "expert": {"ff": self.ff},
                 "router": {"experts": self.experts, "identity": self.identity, "top": self.top, "scale": self.scale}}
 

@@ -18,6 +18,7 @@ from ..config.sopalorn import SopalornConfig
 from ..config.spec import LayerPart, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 UNIT_EPS = 1e-6                 # inside the root that makes the delta rule's queries and keys unit vectors: fixed by the design
+NO_LIMIT = 3.0e38               # a dense feed-forward without a `limit` key clamps nothing
 GATE_ALPHA = 1.702              # the dense feed-forward's gate is g sigmoid(1.702 g): fixed by the design
 
 
@@ -71,7 +72,7 @@ def _mixer(cfg, layer, prefix):
 
 def _feed_forward(mlp, prefix):
     if mlp.kind == "dense":
-        return PartSpec("gated_mlp", {"intermediate_size": mlp.ff, "activation": "clamped_sigmoid", "limit": mlp.limit,
+        return PartSpec("gated_mlp", {"intermediate_size": mlp.ff, "activation": "clamped_sigmoid", "limit": mlp.limit or NO_LIMIT,
                                       "alpha": GATE_ALPHA, "tensors": ("gate", "up", "down")}, prefix)
     return PartSpec("routed_experts",
                     {"n_experts": mlp.experts, "identity": mlp.identity, "top": mlp.top, "intermediate_size": mlp.ff,

@@ -38,7 +38,7 @@ def test_configuration_reads_every_key_and_writes_it_back():
                           (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=26), "rot"),
                           (lambda c: c["layers"][1]["mixer"]["left"]["mask"].update(size=0), "mask"),
                           (lambda c: c["layers"][0]["mixer"].update(kv_heads=4), "kv_heads"),
-                          (lambda c: c["layers"][0]["mlp"].pop("limit"), "limit"),
+                          (lambda c: c["layers"][0]["mlp"].update(limit=-1.0), "limit"),
                           (lambda c: c.update(streams=0), "streams"),
                           (lambda c: c["layers"][1]["mlp"].update(kind="sparse"), "kind")):
         bad = copy.deepcopy(ts.CONFIGS["A"])
